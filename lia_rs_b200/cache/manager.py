@@ -6,7 +6,7 @@ pages per kind of need, and slots of fixed-size per-request state.
 * A *group* collects the caches (one per attention layer that writes one) whose need is the same
   (kv heads, head size, all keys or a window).  A group has one pool of pages and one block table;
   each of its caches has its own K and V tensors [pages, page_size, kv_heads, head_dim] indexed by
-  the same page numbers.  Different groups have pages of their own.
+  the same page numbers (V with the values' head size where the need names one).  Different groups have pages of their own.
 * `ensure(slot, start, end)` makes the pages for positions [start, end) present in every group,
   all or nothing (src/inference/page_cache.rs:184-206).  In a window group the pages that lie
   wholly before `start - window + 1` are given back first: no later token can see them.
@@ -114,8 +114,9 @@ class CacheGroup:
         self.tables = _Tables(self)                        # per slot: page of each logical block, or -1
         self.first_block = _FirstBlocks(self)              # blocks before this were given back
         shape = (num_pages, page_size, request.kv_heads, request.head_dim)
+        v_shape = (num_pages, page_size, request.kv_heads, getattr(request, "v_head_dim", None) or request.head_dim)
         self.k = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
-        self.v = {c: torch.zeros(shape, dtype=dtype, device=device) for c in cache_ids}
+        self.v = {c: torch.zeros(v_shape, dtype=dtype, device=device) for c in cache_ids}
         pin = torch.device(device).type == "cuda"
         # the live table: the native cache writes the entries it changes straight into this memory
         self.host_table = torch.full((max_slots, max_blocks), -1, dtype=torch.int32, pin_memory=pin)

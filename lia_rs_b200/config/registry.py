@@ -3,7 +3,7 @@
 The reference dispatches on config.json's `model_type` with a `match`
 (src/models/mod.rs:41-51) and fails with "unsupported model architecture"; here the table
 is open: `register_architecture` adds an entry, and an architecture is found by the first
-name in config.json's `architectures`, then by `model_type`.
+name in config.json's `architectures`, then by `architecture` (a single name), then by `model_type`.
 """
 from __future__ import annotations
 
@@ -39,6 +39,8 @@ def known_architectures() -> list:
 def resolve_architecture(raw: dict) -> Architecture:
     """The registry entry that config.json (as a dict) names."""
     candidates = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):
+        candidates.append(raw["architecture"])
     if raw.get("model_type"):
         candidates.append(raw["model_type"])
     for name in candidates:

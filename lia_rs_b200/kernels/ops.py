@@ -76,6 +76,17 @@ class _Signatures:
     lia_select_candidates = [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, ctypes.c_longlong, c_void_p]
     lia_select_candidates_scratch_floats = [c_int, c_int, c_int]
+    lia_rotary_pairs_kv_write = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int, c_int, c_int,
+                                 c_void_p, c_void_p]
+    lia_sigmoid_attention_generic = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                     c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lia_short_conv = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+    lia_embedding_positions = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_float, c_void_p, c_void_p]
+    lia_reinject_input = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -587,3 +598,113 @@ def select_candidates(logits, k: int, out_values, out_ids, nonfinite, temperatur
         _check(lib().lia_select_candidates(_p(logits), logits.stride(0), vocab, rows, k, _p(out_values), _p(out_ids),
                                            _p(nonfinite), _p(temperature), _p(mass), _p(scratch), scratch.numel(),
                                            _stream()), "select_candidates")
+
+
+# ---- parts that other attention designs bring: pairwise rotary encoding, attention with sigmoid weights, a short
+# ---- causal convolution behind the norm, learned positions, a re-injection of the embedding output
+
+def embedding_positions(tokens, positions, table, position_table, out, scale: float, copy=None, error_flag=None):
+    """out[t] = table[token_t] * scale + position_table[position_t] (32-bit); `copy` receives the same rows; see
+    csrc/residual_ops.cu."""
+    _cuda(tokens, positions, table, position_table, out, copy, error_flag)
+    n, hidden = out.shape
+    if table.dtype != position_table.dtype or position_table.shape[1] != hidden or table.shape[1] != hidden:
+        raise KernelError("embedding_positions: both tables must have one element type and the stream's width")
+    if out.dtype != torch.float32 or (copy is not None and (copy.dtype != torch.float32 or copy.shape != out.shape)):
+        raise KernelError("embedding_positions writes 32-bit rows")
+    with _timed("embedding"):
+        _check(lib().lia_embedding_positions(_p(tokens), _p(positions), _p(table), _p(position_table),
+                                             dtype_code(table.dtype), _p(out), _p(copy), n, hidden, table.shape[0],
+                                             position_table.shape[0], scale, _p(error_flag), _stream()),
+               "embedding_positions")
+
+
+def reinject_input(x, x0, bias, side_by_side):
+    """side_by_side[t] = [x[t], x0[t]] in its own element type, then x[t] = bias; see csrc/residual_ops.cu."""
+    _cuda(x, x0, bias, side_by_side)
+    n, hidden = x.shape
+    if x.dtype != torch.float32 or x0.dtype != torch.float32 or x0.shape != x.shape or \
+            tuple(side_by_side.shape) != (n, 2 * hidden) or (bias is not None and bias.numel() != hidden):
+        raise KernelError("reinject_input: 32-bit streams of one shape, an output twice as wide, a bias of the width")
+    with _timed("reinject_input"):
+        _check(lib().lia_reinject_input(_p(x), _p(x0), _p(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                        _p(side_by_side), dtype_code(side_by_side.dtype), n, hidden, _stream()),
+               "reinject_input")
+
+
+SHORT_CONV_MAX_TAPS = 8
+
+
+def short_conv(x, norm_weight, taps0, taps1, positions, slots, state, tail, out0, out1, eps: float, single: bool):
+    """RMSNorm of the 32-bit rows `x` and a short causal convolution of the normed rows for up to two readers
+    (`taps0` -> `out0`, `taps1` -> `out1`; either pair may be None), carrying each request's last taps - 1 normed rows
+    in `state` [slots, taps - 1, width]; see csrc/short_conv.cu.  `single`: every request of the step brings one
+    token; otherwise `tail` ([tokens, width] 32-bit scratch) is needed."""
+    _cuda(x, norm_weight, taps0, taps1, positions, slots, state, tail, out0, out1)
+    n, width = x.shape
+    given = [t for t in (taps0, taps1) if t is not None]
+    outs = [o for o in (out0, out1) if o is not None]
+    if not given or (taps0 is None) != (out0 is None) or (taps1 is None) != (out1 is None):
+        raise KernelError("short_conv: taps and outputs come in pairs, at least one")
+    taps = given[0].shape[1]
+    if any(t.shape != (width, taps) or t.dtype != norm_weight.dtype for t in given) or x.dtype != torch.float32:
+        raise KernelError("short_conv: taps are [width, taps] of the norm weight's element type, x is 32-bit")
+    if any(o.shape != x.shape or o.dtype != outs[0].dtype for o in outs):
+        raise KernelError("short_conv: outputs have the shape of x and one element type")
+    if taps > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps - 1, width)):
+        raise KernelError("short_conv: state must be 32-bit [slots, taps - 1, width]")
+    if taps > 1 and not single and (tail is None or tail.dtype != torch.float32 or tail.shape != x.shape):
+        raise KernelError("short_conv: a step with runs of several tokens needs 32-bit scratch of x's shape")
+    with _timed("short_conv", nbytes=x.numel() * 4 + sum(o.numel() * o.element_size() for o in outs)):
+        _check(lib().lia_short_conv(_p(x), _p(norm_weight), _p(taps0), _p(taps1), dtype_code(norm_weight.dtype),
+                                    _p(positions), _p(slots), _p(state), _p(tail), _p(out0), _p(out1),
+                                    dtype_code(outs[0].dtype), n, width, taps, eps, 1 if single else 0, _stream()),
+               "short_conv")
+
+
+def rotary_pairs_kv_write(rows, positions, slots, block_table, q_out, k_pages, v_pages, nq, nkv, d, dv, rotary_dim, freq,
+                          magnitude: float = 1.0, write_kv=True, error_flag=None):
+    """Rotary encoding over adjacent pairs of q and k (rows: 32-bit [tokens, >= (nq + nkv) d + nkv dv]) and append
+    of k and v to the pages; see csrc/rotary_pairs.cu."""
+    _cuda(rows, positions, slots, block_table, q_out, k_pages, v_pages, freq, error_flag)
+    if rows.dtype != torch.float32 or rows.shape[1] < (nq + nkv) * d + nkv * dv:
+        raise KernelError("rotary_pairs_kv_write takes 32-bit rows of q, k and v heads")
+    if q_out.dtype != k_pages.dtype or k_pages.dtype != v_pages.dtype:
+        raise KernelError("rotary_pairs_kv_write: q and the cache must have one element type")
+    if tuple(k_pages.shape[2:]) != (nkv, d) or tuple(v_pages.shape[2:]) != (nkv, dv):
+        raise KernelError("rotary_pairs_kv_write: the pages do not have the heads' sizes")
+    with _timed("rotary_pairs_kv_write"):
+        _check(lib().lia_rotary_pairs_kv_write(_p(rows), rows.stride(0), _p(positions), _p(slots), _p(block_table),
+                                               block_table.shape[1], _p(q_out), _p(k_pages), _p(v_pages),
+                                               dtype_code(q_out.dtype), rows.shape[0], nq, nkv, d, dv, int(rotary_dim),
+                                               _p(freq), float(magnitude), k_pages.shape[1], k_pages.shape[0],
+                                               1 if write_kv else 0, _p(error_flag), _stream()),
+               "rotary_pairs_kv_write")
+
+
+def sigmoid_attention_generic(q, k_pages, v_pages, positions, slots, block_table, out, nq, nkv, d, dv, window, chunk,
+                              scale, head_bias=None, gate=None, gate_stride=0, rows=None, error_flag=None, label=None,
+                              work_bytes=0):
+    """Attention with sigmoid weights (no softmax) for every token of the batch or for the batch indices in `rows`;
+    see csrc/sigmoid_attention.cu.  `head_bias` [nq] 32-bit is added to every score of its head; `gate` is a 32-bit
+    tensor in which token t's head h has its output-gate logit at flat index t * gate_stride + h."""
+    _cuda(q, k_pages, v_pages, positions, slots, block_table, out, rows, head_bias, error_flag)
+    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype):
+        raise KernelError("attention: q, cache and out must have one element type")
+    if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != nq):
+        raise KernelError("sigmoid attention: head_bias must be 32-bit, one per query head")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda):
+        raise KernelError("sigmoid attention: gate logits must be 32-bit")
+    n = q.shape[0] if rows is None else rows.shape[0]
+    with _timed("sigmoid_attention_generic", label, work_bytes):
+        _check(lib().lia_sigmoid_attention_generic(_p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(positions),
+                                                   _p(slots), _p(block_table), block_table.shape[1], _p(rows), _p(out),
+                                                   n, nq, nkv, d, dv, k_pages.shape[1], int(window or 0), int(chunk or 0),
+                                                   scale, _p(head_bias), _p(gate), int(gate_stride), k_pages.shape[0],
+                                                   _p(error_flag), _stream()),
+               "sigmoid_attention_generic")
+
+
+def sigmoid_attention_tc_accepts(group: int, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel for sigmoid attention takes these sizes (bfloat16)."""
+    return False

@@ -1,4 +1,4 @@
 from .decoder import DecoderModel, ModelSpec, ScheduleEntry
-from . import minicpm5_llama  # noqa: F401  (registers the architecture)
+from . import minicpm5_llama, nafevik  # noqa: F401  (register the architectures)
 
 __all__ = ["DecoderModel", "ModelSpec", "ScheduleEntry"]

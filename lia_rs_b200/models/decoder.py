@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from ..parts import NORMS, PartSpec, build_layer, check_layer, layer_tensor_specs, lookup, MIXERS
+from ..parts import ARRANGEMENTS, JUNCTIONS, NORMS, PartSpec, build_layer, check_layer, layer_tensor_specs, lookup, MIXERS
 from ..parts.linear import STORE, linear, prepare_weight
 from ..weights import TensorSpec
 
@@ -41,6 +41,8 @@ class ModelSpec:
     layer_prefix: str = "model.layers.{}."
     final_norm_prefix: str = "model.norm."
     eos_token_ids: tuple = ()
+    position_table_name: Optional[str] = None       # a learned vector per position [max_positions, hidden], added to the embedding
+    junctions: dict = field(default_factory=dict)   # schedule position -> PartSpec of a junction that runs ahead of that entry
 
     def __post_init__(self):
         if not self.schedule:
@@ -52,6 +54,10 @@ class ModelSpec:
                 raise ValueError(f"schedule names layer {entry.layer}, the model has {len(self.layers)}")
         for layer in self.layers:
             check_layer(layer)                      # a size that a part or its kernels cannot take is refused here
+        for position, junction in self.junctions.items():
+            if not 0 <= position < len(self.schedule):
+                raise ValueError(f"a junction is attached to schedule position {position}, the schedule has {len(self.schedule)}")
+            lookup(JUNCTIONS, junction.kind, "junction").check_params(junction.params)
         requests = {}
         writers = set()
         for entry in self.schedule:
@@ -74,6 +80,15 @@ class ModelSpec:
 
     def tensor_specs(self) -> list:
         specs = [TensorSpec(self.embedding_name, (self.vocab_size, self.hidden_size))]
+        if self.position_table_name is not None:
+            specs.append(TensorSpec(self.position_table_name, (self.max_positions, self.hidden_size)))
+        seen = set()
+        for position in sorted(self.junctions):
+            junction = self.junctions[position]
+            for spec in lookup(JUNCTIONS, junction.kind, "junction").tensor_specs(junction.params, ""):
+                if spec.name not in seen:             # junctions may share tensors (one weight for every pass)
+                    seen.add(spec.name)
+                    specs.append(spec)
         for i, layer in enumerate(self.layers):
             specs += layer_tensor_specs(layer, self.layer_prefix.format(i))
         specs += lookup(NORMS, self.final_norm.kind, "norm").tensor_specs(self.final_norm.params,
@@ -91,12 +106,17 @@ class ModelSpec:
         return out
 
     def state_requests(self) -> dict:
-        """schedule position -> StateRequest, for mixers that keep per-request state."""
+        """state id -> StateRequest: the schedule position for a mixer that keeps per-request state, ("layer",
+        schedule position) for an arrangement that does.  A layer that runs twice has a state for each run."""
         out = {}
         for position, entry in enumerate(self.schedule):
-            request = self._mixer(entry.layer).state_request(self.layers[entry.layer].mixer.params)
+            layer = self.layers[entry.layer]
+            request = self._mixer(entry.layer).state_request(layer.mixer.params)
             if request is not None:
                 out[position] = request
+            request = lookup(ARRANGEMENTS, layer.arrangement, "arrangement").state_request(layer)
+            if request is not None:
+                out[("layer", position)] = request
         return out
 
 
@@ -110,6 +130,15 @@ class DecoderModel:
 
         table = tensors[spec.embedding_name].to(device)
         self.embedding = prepare_weight(table, runtime)
+        self.position_table = None
+        if spec.position_table_name is not None:
+            self.position_table = prepare_weight(tensors[spec.position_table_name].to(device), runtime)
+        self.junctions = {}
+        for position, junction in spec.junctions.items():
+            cls = lookup(JUNCTIONS, junction.kind, "junction")
+            names = [s.name for s in cls.tensor_specs(junction.params, "")]
+            self.junctions[position] = cls(junction.params, on_device(names), "", runtime)
+        self._keeps_first = any(j.needs_first for j in self.junctions.values())
         self.layers = []
         for i, layer in enumerate(spec.layers):
             prefix = spec.layer_prefix.format(i)
@@ -126,9 +155,12 @@ class DecoderModel:
         distinct = {}
         for layer_spec, layer in zip(spec.layers, self.layers):
             distinct.setdefault(repr(layer_spec), layer)
-        self._key_layers = list(distinct.values()) + [self.final_norm]
+        self._key_layers = list(distinct.values()) + [self.final_norm] + list(self.junctions.values())
+        self._own_state = [lookup(ARRANGEMENTS, spec.layers[entry.layer].arrangement, "arrangement").state_request(
+            spec.layers[entry.layer]) is not None for entry in spec.schedule]
         # decode steps may be captured in CUDA graphs only if every part launches the same way each step
-        self.graph_safe = all(layer.graph_safe for layer in self.layers) and bool(self.final_norm.graph_safe)
+        self.graph_safe = (all(layer.graph_safe for layer in self.layers) and bool(self.final_norm.graph_safe)
+                           and all(j.graph_safe for j in self.junctions.values()))
 
     def graph_key(self, ctx) -> tuple:
         """What a captured step is good for: the step's numbers of tokens, of wanted rows, of single-token entries
@@ -150,16 +182,27 @@ class DecoderModel:
         rt, spec = self.runtime, self.spec
         n = ctx.n_tokens
         h = ctx.buffer("model.h", (n, spec.hidden_size), torch.float32)
-        rt.ops.embedding(ctx.tokens, self.embedding, h, spec.embedding_scale, ctx.error_flag)
+        first = ctx.buffer("model.h0", (n, spec.hidden_size), torch.float32) if self._keeps_first else None
+        if self.position_table is not None:
+            rt.ops.embedding_positions(ctx.tokens, ctx.positions, self.embedding, self.position_table, h,
+                                       spec.embedding_scale, copy=first, error_flag=ctx.error_flag)
+        else:
+            rt.ops.embedding(ctx.tokens, self.embedding, h, spec.embedding_scale, ctx.error_flag)
+            if first is not None:
+                first.copy_(h)
         picked = None
         last = len(spec.schedule) - 1
         for position, entry in enumerate(spec.schedule):
+            junction = self.junctions.get(position)
+            if junction is not None:
+                junction.forward(ctx, h, first)
             kv = ctx.kv_view(entry.cache, entry.writes) if entry.cache is not None else None
             layer = self.layers[entry.layer]
+            more = {"own_state": ctx.state(("layer", position))} if self._own_state[position] else {}
             if position == last and ctx.n_out < n and getattr(layer, "supports_rows", False):
-                picked = layer.forward(ctx, h, kv=kv, state=ctx.state(position), rows=ctx.out_rows, n_rows=ctx.n_out)
+                picked = layer.forward(ctx, h, kv=kv, state=ctx.state(position), rows=ctx.out_rows, n_rows=ctx.n_out, **more)
             else:
-                layer.forward(ctx, h, kv=kv, state=ctx.state(position))
+                layer.forward(ctx, h, kv=kv, state=ctx.state(position), **more)
         if ctx.n_out == 0:
             return ctx.logits_buffer(0, spec.vocab_size)
         y = ctx.buffer("model.y", (ctx.n_out, spec.hidden_size), rt.compute_dtype)

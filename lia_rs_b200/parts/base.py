@@ -9,6 +9,8 @@ of four kinds of parts:
   norm               normalises rows of the residual stream
   position encoding  how positions enter the mixer (rotary here)
 
+Between layers a model may place *junctions* (a re-injection of the embedding output, for instance).
+
 Every part is built from a `PartSpec` (its kind and its parameters: all sizes and constants)
 and from the tensors it declared.  No part knows which model it is in: the model builder
 (`models/`) chooses the parts layer by layer from the configuration.
@@ -35,10 +37,14 @@ class PartSpec:
 @dataclass(frozen=True)
 class KVCacheRequest:
     """What a mixer needs from the paged cache: `kv_heads` x `head_dim` keys and values per
-    token, all of them (`window` None) or the last `window` of them."""
+    token, all of them (`window` None) or the last `window` of them.  `v_head_dim`: the values' head size where
+    it differs from the keys'.  `chunk`: a token only ever reads the keys of its own block of `chunk` positions
+    (blocks counted from position 0), so the pages that lie wholly before a request's current block are given back."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -185,6 +191,12 @@ class Arrangement:
 
     graph_safe = False
 
+    @staticmethod
+    def state_request(layer_spec) -> Optional[StateRequest]:
+        """Per-request state of the arrangement itself (beside its mixer's), or None.  An arrangement that asks
+        for one is handed the tensor [slots, *shape] as `own_state` at every `forward`."""
+        return None
+
     def graph_key(self, ctx) -> tuple:
         """As `Part.graph_key`, for the layer: what its parts answer, put together.  The default is the answer that
         is always right."""
@@ -209,7 +221,18 @@ class Arrangement:
         raise NotImplementedError
 
 
+class Junction(Part):
+    """Something that happens to the residual stream between two layers (ahead of the schedule entry it is
+    attached to): `forward(ctx, residual, first)` changes `residual` in place; `first` is the embedding output of
+    the step's tokens (32-bit, kept by the model for the junctions that set `needs_first`)."""
+    needs_first = False
+
+    def forward(self, ctx, residual: torch.Tensor, first: Optional[torch.Tensor]):
+        raise NotImplementedError
+
+
 MIXERS: dict = {}
+JUNCTIONS: dict = {}
 FEED_FORWARDS: dict = {}
 NORMS: dict = {}
 POSITION_ENCODINGS: dict = {}
@@ -242,6 +265,10 @@ def register_position_encoding(kind: str):
 
 def register_arrangement(kind: str):
     return _register(ARRANGEMENTS, kind)
+
+
+def register_junction(kind: str):
+    return _register(JUNCTIONS, kind)
 
 
 def lookup(table: dict, kind: str, what: str):

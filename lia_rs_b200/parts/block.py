@@ -7,8 +7,12 @@ Llama).  Checkpoint names: input_layernorm, self_attn, post_attention_layernorm,
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Optional
 
-from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Arrangement, DeferredNorm, PartSpec, lookup,
+import torch
+
+from ..weights import TensorSpec
+from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, Arrangement, DeferredNorm, PartSpec, StateRequest, lookup,
                    register_arrangement)
 
 
@@ -17,11 +21,12 @@ class LayerSpec:
     """`norm` is the norm at every place of the arrangement; `norms` names other norms for single places
     (for the pre-norm arrangement the places are "norm1" and "norm2")."""
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]     # None: the layer has no feed-forward (an arrangement that allows it)
     norm: PartSpec
     arrangement: str = "prenorm"
     residual_scale: float = 1.0
     norms: dict = field(default_factory=dict, hash=False, compare=False)
+    options: dict = field(default_factory=dict, hash=False, compare=False)      # what else the arrangement is told
     names: dict = field(default_factory=lambda: {"norm1": "input_layernorm.", "mixer": "self_attn.",
                                                  "norm2": "post_attention_layernorm.", "feed_forward": "mlp."},
                         hash=False, compare=False)
@@ -91,6 +96,129 @@ class PreNormBlock(Arrangement):
                 self.runtime.ops.gather_rows(residual, rows, picked)
         if n_rows:
             self.feed_forward.forward(ctx, self._normed(ctx, self.norm2, self.feed_forward, picked), picked, self.scale)
+        return picked
+
+
+@register_arrangement("parallel")
+class ParallelBlock(Arrangement):
+    """One norm, both sublayers read its output, one residual sum:
+
+        h = norm(x);   x <- x + s * (mixer(a(h)) + feed_forward(b(h)))
+
+    a and b are the identity, or, with `options["input_conv"] = {"taps": n, "names": (mixer's, feed-forward's)}`,
+    a short causal convolution over time on each channel added to its input, y_t = h_t + sum_j c[:, j] h_(t-n+1+j)
+    (c [hidden, n], zeros before the sequence's start), with taps of its own for each sublayer.  The last n - 1
+    normed rows of a request are the arrangement's state (one tensor for both sublayers: they read the same rows).
+    The norm must be an RMSNorm (`rms_record`): norm and convolution are one kernel (csrc/short_conv.cu).  The
+    feed-forward may be absent.  Checkpoint names: `names["norm1"]`, `names["mixer"]`, `names["feed_forward"]`."""
+    supports_rows = True
+
+    @staticmethod
+    def _classes(spec: LayerSpec):
+        norm = spec.norm_at("norm1")
+        out = [(lookup(NORMS, norm.kind, "norm"), norm.params), (lookup(MIXERS, spec.mixer.kind, "mixer"), spec.mixer.params)]
+        if spec.feed_forward is not None:
+            out.append((lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward"), spec.feed_forward.params))
+        return out
+
+    @staticmethod
+    def _conv(spec: LayerSpec):
+        conv = spec.options.get("input_conv")
+        if not conv:
+            return 0, ()
+        names = tuple(conv["names"])[:2 if spec.feed_forward is not None else 1]
+        return int(conv["taps"]), names
+
+    @staticmethod
+    def check(spec: LayerSpec) -> None:
+        for cls, params in ParallelBlock._classes(spec):
+            cls.check_params(params)
+        taps, _ = ParallelBlock._conv(spec)
+        if taps and not 1 <= taps <= 8:
+            raise ValueError(f"input convolution: {taps} taps; the kernel takes 1..8")
+
+    @staticmethod
+    def _hidden(spec: LayerSpec) -> int:
+        return int(spec.norm_at("norm1").params["hidden"])
+
+    @staticmethod
+    def tensor_specs(spec: LayerSpec, prefix: str) -> list:
+        n = spec.names
+        places = (n["norm1"], n["mixer"], n["feed_forward"])
+        out = [t for (cls, params), place in zip(ParallelBlock._classes(spec), places)
+               for t in cls.tensor_specs(params, prefix + place)]
+        taps, names = ParallelBlock._conv(spec)
+        return out + [TensorSpec(prefix + name, (ParallelBlock._hidden(spec), taps)) for name in names]
+
+    @staticmethod
+    def state_request(spec: LayerSpec):
+        taps, _ = ParallelBlock._conv(spec)
+        return StateRequest((taps - 1, ParallelBlock._hidden(spec)), torch.float32) if taps > 1 else None
+
+    def __init__(self, spec: LayerSpec, tensors: dict, prefix: str, runtime):
+        n = spec.names
+        self.runtime = runtime
+        self.scale = float(spec.residual_scale)
+        places = (n["norm1"], n["mixer"], n["feed_forward"])
+        parts = [cls(params, tensors, prefix + place, runtime) for (cls, params), place in zip(self._classes(spec), places)]
+        self.norm, self.mixer = parts[0], parts[1]
+        self.feed_forward = parts[2] if len(parts) > 2 else None
+        self.hidden = self._hidden(spec)
+        self.taps, names = self._conv(spec)
+        self.conv_weights = []
+        if self.taps:
+            record = self.norm.rms_record()
+            if record is None:
+                raise ValueError("the parallel arrangement's input convolution needs an RMSNorm")
+            self.norm_weight, self.eps = record
+            self.conv_weights = [tensors[prefix + name].to(self.norm_weight.dtype).contiguous() for name in names]
+        self.graph_safe = all(part.graph_safe for part in parts)
+
+    def graph_key(self, ctx) -> tuple:
+        key = self.norm.graph_key(ctx) + self.mixer.graph_key(ctx)
+        return key + (self.feed_forward.graph_key(ctx) if self.feed_forward is not None else ())
+
+    def _inputs(self, ctx, residual, own_state):
+        """(the mixer's input, the feed-forward's input) in the compute element type."""
+        rt, n = self.runtime, residual.shape[0]
+        a = ctx.buffer("block.x", (n, self.hidden), rt.compute_dtype)
+        if not self.taps:
+            self.norm.forward(ctx, residual, a)
+            return a, a
+        b = ctx.buffer("block.x2", (n, self.hidden), rt.compute_dtype) if self.feed_forward is not None else None
+        single = ctx.decode_only
+        tail = None if single or self.taps <= 1 else ctx.buffer("block.conv_tail", (n, self.hidden), torch.float32)
+        rt.ops.short_conv(residual, self.norm_weight, self.conv_weights[0],
+                          self.conv_weights[1] if b is not None else None, ctx.positions, ctx.slots, own_state, tail,
+                          a, b, self.eps, single)
+        return a, b
+
+    def forward(self, ctx, residual, kv=None, state=None, rows=None, n_rows=None, own_state=None):
+        a, b = self._inputs(ctx, residual, own_state)
+        if rows is None:
+            self.mixer.forward(ctx, a, residual, self.scale, kv=kv, state=state)
+            if self.feed_forward is not None:
+                self.feed_forward.forward(ctx, b, residual, self.scale)
+            return None
+        # only `rows` matter after this layer: cache and state have been brought up to date for every token above and
+        # in the mixer; the output projection, the feed-forward and the residual sum run on the picked rows alone
+        picked = ctx.buffer("block.picked", (n_rows, residual.shape[1]), residual.dtype)
+        if n_rows:
+            self.runtime.ops.gather_rows(residual, rows, picked)
+        if self.mixer.supports_rows:
+            self.mixer.forward(ctx, a, picked, self.scale, kv=kv, state=state, rows=rows, n_rows=n_rows)
+        else:
+            full = ctx.buffer("block.mixed", tuple(residual.shape), residual.dtype)
+            full.zero_()
+            self.mixer.forward(ctx, a, full, self.scale, kv=kv, state=state)
+            if n_rows:
+                mixed = ctx.buffer("block.mixed_rows", (n_rows, residual.shape[1]), residual.dtype)
+                self.runtime.ops.gather_rows(full, rows, mixed)
+                picked.add_(mixed)
+        if n_rows and self.feed_forward is not None:
+            b_rows = ctx.buffer("block.x2_rows", (n_rows, self.hidden), self.runtime.compute_dtype)
+            self.runtime.ops.gather_rows(b, rows, b_rows)
+            self.feed_forward.forward(ctx, b_rows, picked, self.scale)
         return picked
 
 

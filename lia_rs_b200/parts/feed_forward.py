@@ -2,7 +2,8 @@
 (src/inference/moe.rs:31-61, src/gpu/kernels/basic.rs:150-157).  Gate and up are one product
 against [Wg; Wu] whose epilogue applies the activation (the reference's gated kernel does the
 same with two matrices: src/gpu/kernels/llama_gated.rs:181-222); the down product adds into the
-residual stream.  Parameters: hidden, intermediate."""
+residual stream.  Parameters: hidden, intermediate, and optionally `names`: the checkpoint names of the gate, up
+and down matrices behind the part's prefix."""
 from __future__ import annotations
 
 import torch
@@ -20,19 +21,25 @@ class SwiGLU(FeedForward):
         return ()                    # rows in, rows out: only the number of tokens matters
     takes_deferred_norm = True
 
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    @staticmethod
+    def _names(params, prefix):
+        names = {**SwiGLU.NAMES, **params.get("names", {})}
+        return prefix + names["gate"], prefix + names["up"], prefix + names["down"]
+
     @staticmethod
     def tensor_specs(params, prefix):
         h, i = params["hidden"], params["intermediate"]
-        return [TensorSpec(prefix + "gate_proj.weight", (i, h)),
-                TensorSpec(prefix + "up_proj.weight", (i, h)),
-                TensorSpec(prefix + "down_proj.weight", (h, i))]
+        gate, up, down = SwiGLU._names(params, prefix)
+        return [TensorSpec(gate, (i, h)), TensorSpec(up, (i, h)), TensorSpec(down, (h, i))]
 
     def __init__(self, params, tensors, prefix, runtime):
         super().__init__(params, tensors, prefix, runtime)
         self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
-        self.w_gate_up = prepare_weight(torch.cat([tensors[prefix + "gate_proj.weight"],
-                                                   tensors[prefix + "up_proj.weight"]], dim=0), runtime)
-        self.w_down = prepare_weight(tensors[prefix + "down_proj.weight"], runtime)
+        gate, up, down = self._names(params, prefix)
+        self.w_gate_up = prepare_weight(torch.cat([tensors[gate], tensors[up]], dim=0), runtime)
+        self.w_down = prepare_weight(tensors[down], runtime)
 
     def forward(self, ctx, x, residual, scale):
         rt, n = self.runtime, x.shape[0]
