@@ -1,0 +1,252 @@
+"""Each new mechanism alone, its kernel against the plain implementation's function (tests/plain_nafevik.py): learned
+positions, the re-injection's input, the norm with its short convolution and carried state, the pairwise rotary
+encoding with scaled frequencies, and the sigmoid attention over a paged cache, with inputs made so that ONE key
+decides the output: far back, at page borders, just inside and just outside a block or a window, in prompt portions
+and in single decoded tokens."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_nafevik as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from lia_rs_b200.kernels import ops as module
+    module.lib()
+    return module
+
+
+def i32(values):
+    return torch.tensor(list(values), dtype=torch.int32, device=DEV)
+
+
+def close(actual, reference, dtype, what):
+    actual, reference = actual.double().cpu(), reference.double()
+    scale = max(1.0, float(reference.abs().max()))
+    limit = (2e-5 if dtype == torch.float32 else 1.2e-2) * scale
+    worst = float((actual - reference).abs().max())
+    assert worst <= limit, f"{what}: {worst:.3e} > {limit:.3e}"
+
+
+def test_embedding_with_learned_positions_and_reinjection_input():
+    o = ops()
+    g = torch.Generator().manual_seed(0)
+    vocab, width, most = 53, 40, 31
+    table = torch.randn(vocab, width, generator=g).to(torch.bfloat16)
+    where = torch.randn(most, width, generator=g).to(torch.bfloat16)
+    tokens, positions = [5, 52, 0, 17, 17], [0, 30, 7, 8, 3]
+    out = torch.empty(5, width, dtype=torch.float32, device=DEV)
+    copy = torch.empty_like(out)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.embedding_positions(i32(tokens), i32(positions), table.to(DEV), where.to(DEV), out, 1.0, copy=copy, error_flag=flag)
+    want = table.double()[tokens] + where.double()[positions]
+    assert torch.equal(out.cpu().double(), want) and torch.equal(copy, out) and int(flag.item()) == 0
+    o.embedding_positions(i32([1]), i32([most]), table.to(DEV), where.to(DEV), out[:1], 1.0, error_flag=flag)
+    assert int(flag.item()) == 1                                   # a position beyond the table is refused, not read
+    for dtype in DTYPES:
+        x = torch.randn(5, width, generator=g).to(DEV)
+        first = torch.randn(5, width, generator=g).to(DEV)
+        bias = torch.randn(width, generator=g).to(torch.bfloat16).to(DEV)
+        both = torch.empty(5, 2 * width, dtype=dtype, device=DEV)
+        before = x.clone()
+        o.reinject_input(x, first, bias, both)
+        assert torch.equal(both, torch.cat([before, first], dim=1).to(dtype))
+        assert torch.equal(x, bias.float().expand(5, width))
+
+
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_and_short_convolution_with_carried_state(taps, dtype):
+    """Three requests in three slots; their sequences come in steps of unequal runs (a run shorter than the taps, a
+    run of one, single-token steps that move the state in the same kernel, rows of nobody).  Every output row equals
+    the plain convolution of the whole sequence."""
+    o = ops()
+    g = torch.Generator().manual_seed(taps)
+    width, eps, slots = 72, 1e-5, 4
+    norm_w = (1 + 0.3 * torch.randn(width, generator=g)).to(torch.bfloat16)
+    c = [(0.7 * torch.randn(width, taps, generator=g)).to(torch.bfloat16) for _ in range(2)]
+    lengths = {0: 23, 2: 9, 3: 14}
+    x = {s: torch.randn(n, width, generator=g) * (1 + s) for s, n in lengths.items()}
+    want = {}
+    for s in lengths:
+        h = plain.rms_norm(x[s].double(), norm_w, eps)
+        want[s] = [plain.input_conv(h, c[0]), plain.input_conv(h, c[1])]
+    state = torch.full((slots, max(taps - 1, 1), width), 7.0, device=DEV)[:, :taps - 1].contiguous()   # junk: zeroing is not relied on
+    at = {s: 0 for s in lengths}
+    got = {s: [[], []] for s in lengths}
+    steps = [[(0, 1), (2, 2)], [(2, 1), (0, 1), (3, 1)], [(3, 1), (0, 1)], [(0, 5), (3, 2), (2, 1)], [(2, 1), (0, 1), (3, 1)],
+             [(0, 14), (2, 4), (3, 9)]]
+    for step in steps:
+        rows, positions, slot_ids = [], [], []
+        for s, count in step:
+            rows.append(x[s][at[s]:at[s] + count])
+            positions += range(at[s], at[s] + count)
+            slot_ids += [s] * count
+        single = all(count == 1 for _, count in step)
+        if single:                                                   # rows of nobody behind a step of single tokens
+            rows.append(torch.randn(2, width, generator=g))
+            positions += [0, 0]
+            slot_ids += [-1, -1]
+        batch = torch.cat(rows).to(DEV)
+        n = batch.shape[0]
+        out = [torch.empty(n, width, dtype=dtype, device=DEV) for _ in range(2)]
+        tail = torch.empty(n, width, device=DEV)
+        o.short_conv(batch, norm_w.to(DEV), c[0].to(DEV), c[1].to(DEV), i32(positions), i32(slot_ids), state if taps > 1 else None,
+                     tail, out[0], out[1], eps, single)
+        row = 0
+        for s, count in step:
+            for r in range(2):
+                got[s][r].append(out[r][row:row + count])
+            at[s] += count
+            row += count
+    for s in lengths:
+        assert at[s] == lengths[s]
+        for r in range(2):
+            close(torch.cat(got[s][r]), want[s][r], dtype, f"taps {taps} slot {s} reader {r}")
+    # one reader alone (a layer without a feed-forward)
+    batch = x[0][:6].to(DEV)
+    alone = torch.empty(6, width, dtype=dtype, device=DEV)
+    o.short_conv(batch, norm_w.to(DEV), c[1].to(DEV), None, i32(range(6)), i32([1] * 6), state if taps > 1 else None,
+                 torch.empty(6, width, device=DEV), alone, None, eps, False)
+    close(alone, want[0][1][:6], dtype, "one reader")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,dv,dims,scaling", [(16, 16, 16, None), (48, 24, 32, {"factor": 4.0, "original": 40, "fast": 8.0, "slow": 1.0}),
+                                               (64, 128, 0, None), (40, 8, 40, {"factor": 16.0, "original": 16, "fast": 4.0, "slow": 2.0})])
+def test_pairwise_rotary_encoding_and_append(d, dv, dims, scaling, dtype):
+    from lia_rs_b200.parts.rotary import scaled_frequencies
+    o = ops()
+    g = torch.Generator().manual_seed(d)
+    nq, nkv, page, pages = 3, 2, 4, 9
+    base = 300.0
+    if dims:
+        freq, magnitude = scaled_frequencies(base, dims, scaling)
+        want_freq, want_magnitude = plain.rotary_frequencies(base, dims, scaling)
+        assert torch.allclose(freq, want_freq, rtol=1e-14, atol=0) and abs(magnitude - want_magnitude) < 1e-15
+        if scaling:
+            assert not torch.allclose(freq, plain.rotary_frequencies(base, dims)[0])      # the scaling does something
+    else:
+        freq, magnitude = None, 1.0
+    positions = [0, 1, 2, 33, 34, 5]
+    slot_ids = [0, 0, 0, 1, 1, -1]
+    n = len(positions)
+    stride = (nq + nkv) * d + nkv * dv + 5                         # the rows hold more than q, k and v
+    rows = torch.randn(n, stride, generator=g)
+    table = torch.full((2, 12), -1, dtype=torch.int32)
+    table[0, 0], table[1, 8] = 7, 2
+    k_pages = torch.zeros(pages, page, nkv, d, dtype=dtype, device=DEV)
+    v_pages = torch.zeros(pages, page, nkv, dv, dtype=dtype, device=DEV)
+    q_out = torch.zeros(n, nq * d, dtype=dtype, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.rotary_pairs_kv_write(rows.to(DEV), i32(positions), i32(slot_ids), table.to(DEV), q_out, k_pages, v_pages, nq, nkv, d, dv,
+                            dims, None if freq is None else freq.float().to(DEV), magnitude, error_flag=flag)
+    assert int(flag.item()) == 0
+    q = rows[:, :nq * d].double().view(n, nq, d)
+    k = rows[:, nq * d:(nq + nkv) * d].double().view(n, nkv, d)
+    v = rows[:, (nq + nkv) * d:(nq + nkv) * d + nkv * dv].double().view(n, nkv, dv)
+    if dims:
+        where = torch.tensor(positions)
+        q, k = plain.rotate_pairs(q, where, want_freq, want_magnitude, dims), plain.rotate_pairs(k, where, want_freq, want_magnitude, dims)
+    close(q_out[:5].view(5, nq, d), q[:5], dtype, "q")
+    for t, (p, s) in enumerate(zip(positions[:5], slot_ids[:5])):
+        page_of = int(table[s, p // page])
+        close(k_pages[page_of, p % page], k[t], dtype, f"k of token {t}")
+        close(v_pages[page_of, p % page], v[t], dtype, f"v of token {t}")
+    assert float(q_out[5].abs().max()) == 0.0                     # a row of nobody is skipped
+    untouched = torch.ones(pages, dtype=torch.bool)
+    untouched[[7, 2]] = False
+    assert float(k_pages[untouched].abs().max()) == 0.0 and float(v_pages[untouched].abs().max()) == 0.0
+
+
+def _paged(keys, values, page, pages, order, dtype):
+    """Keys [T, G, d] and values [T, G, dv] of one request laid into pages in the given order of page numbers."""
+    T = keys.shape[0]
+    k_pages = torch.zeros(pages, page, keys.shape[1], keys.shape[2], dtype=dtype, device=DEV)
+    v_pages = torch.zeros(pages, page, values.shape[1], values.shape[2], dtype=dtype, device=DEV)
+    table = torch.full((1, (T + page - 1) // page + 2), -1, dtype=torch.int32)
+    for block in range((T + page - 1) // page):
+        table[0, block] = order[block]
+        rows = slice(block * page, min(T, (block + 1) * page))
+        k_pages[order[block], :rows.stop - rows.start] = keys[rows].to(dtype)
+        v_pages[order[block], :rows.stop - rows.start] = values[rows].to(dtype)
+    return k_pages, v_pages, table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,d,dv,chunk,window,page", [(4, 2, 16, 16, 24, None, 8), (3, 1, 48, 24, 50, None, 16), (2, 2, 64, 64, None, 37, 4),
+                                                        (6, 2, 32, 40, 128, 100, 16), (8, 1, 128, 128, 64, None, 16), (1, 1, 8, 200, None, None, 4)])
+def test_sigmoid_attention_one_key_decides(H, G, d, dv, chunk, window, page, dtype):
+    """The heads' biases push every weight to nothing (sigmoid(-14)); one key per probe is made to score +14 against
+    the probing query, so the output is that key's value if the key is visible and nothing if it is not.  Probes:
+    the token itself, its predecessor, a far key, the first key of the token's block and the key before it, the
+    oldest key of the window and the one before it, the keys on both sides of a page border.  Then random inputs
+    against the plain function, for a prompt portion and for the same tokens one by one."""
+    o = ops()
+    g = torch.Generator().manual_seed(H * 100 + d)
+    T, scale = 300, 0.5
+    bias = torch.full((H,), -14.0)
+    gate = torch.randn(T, H, generator=g)
+    values = torch.randn(T, G, dv, generator=g)
+    pages = (T + page - 1) // page + 3
+    order = torch.randperm(pages, generator=g).tolist()
+    probes = []
+    for p in (0, 1, 129, 255, 299):
+        first = 0
+        if chunk:
+            first = max(first, p // chunk * chunk)
+        if window:
+            first = max(first, p - window + 1)
+        border = p // page * page
+        for j in {p, p - 1, first, first - 1, first + 1, border, border - 1, p - 100, 0}:
+            if 0 <= j <= p:
+                probes.append((p, j, plain.visible(p, j, chunk, window)))
+    if chunk or window:
+        assert any(not seen for _, _, seen in probes)
+    else:
+        assert any(seen and p - j >= 100 for p, j, seen in probes)          # nothing hides a key hundreds back
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for p, j, seen in probes:
+        keys = torch.randn(T, G, d, generator=g) * 0.05
+        query = torch.randn(H, d, generator=g)
+        query = query / query.norm(dim=-1, keepdim=True)
+        for kvh in range(G):                                         # the kv head's key j points along its first query head
+            keys[j, kvh] = query[kvh * (H // G)] * (28.0 / scale)
+        for h in range(H):
+            query[h] = query[h // (H // G) * (H // G)]
+        k_pages, v_pages, table = _paged(keys, values, page, pages, order, dtype)
+        q = query.view(1, H * d).to(dtype).to(DEV)
+        out = torch.empty(1, H * dv, dtype=dtype, device=DEV)
+        o.sigmoid_attention_generic(q, k_pages, v_pages, i32([p]), i32([0]), table, out, H, G, d, dv, window, chunk, scale,
+                                    bias.to(DEV), gate[p:p + 1].contiguous().to(DEV), H, error_flag=flag)
+        got = out.view(H, dv).float().cpu()
+        for h in range(H):
+            want = values[j, h // (H // G)] * torch.sigmoid(gate[p, h]) if seen else torch.zeros(dv)
+            assert float((got[h] - want).abs().max()) <= 0.03 * max(1.0, float(want.abs().max())), (p, j, seen, h)
+    # random inputs, moderate scores: a prompt portion of all tokens, then single tokens, against the plain function
+    keys = torch.randn(T, G, d, generator=g)
+    query = torch.randn(T, H, d, generator=g)
+    bias = torch.rand(H, generator=g) * 3 - 2.5
+    scale = 1.0 / math.sqrt(d)
+    store = plain.exact if dtype == torch.float32 else plain.to_bf16
+    want = plain.sigmoid_attention(store(query.double()), store(keys.double()), store(values.double()), scale, bias, gate.double(),
+                                   chunk=chunk, window=window)
+    k_pages, v_pages, table = _paged(keys, values, page, pages, order, dtype)
+    q = query.view(T, H * d).to(dtype).to(DEV)
+    out = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
+    wide = torch.cat([torch.randn(T, 3, generator=g), gate], dim=1).contiguous().to(DEV)      # gate logits inside wider rows
+    o.sigmoid_attention_generic(q, k_pages, v_pages, i32(range(T)), i32([0] * T), table, out, H, G, d, dv, window, chunk, scale,
+                                bias.to(DEV), wide[:, 3:], H + 3, error_flag=flag)
+    close(out.view(T, H, dv), want, dtype, "portion")
+    picked = [0, 1, chunk or 7, (chunk or 7) - 1, 130, 299]
+    one = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
+    o.sigmoid_attention_generic(q, k_pages, v_pages, i32(range(T)), i32([0] * T), table, one, H, G, d, dv, window, chunk, scale,
+                                bias.to(DEV), wide[:, 3:], H + 3, rows=i32(picked), error_flag=flag)
+    assert torch.equal(one[picked], out[picked]) and float(one[2].abs().max()) == 0.0
+    assert int(flag.item()) == 0
