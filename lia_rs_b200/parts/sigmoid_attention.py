@@ -49,13 +49,16 @@ class PagedSigmoidAttention:
         self.window, self.chunk, self.scale = window, chunk, float(scale)
         self.head_bias = head_bias
         self.group = self.nq // self.nkv
-        self.variant = "tensor" if dtype == torch.bfloat16 and ops.sigmoid_attention_tc_accepts(
-            self.group, self.d, self.dv) else "generic"
+        self.per_tile = ops.sigmoid_attention_tc_tokens_per_tile(self.group, self.d, self.dv) if dtype == torch.bfloat16 else 0
+        self.variant = "tensor" if self.per_tile else "generic"
 
     def graph_key(self, ctx) -> tuple:
-        if self.variant != "tensor":
+        """What of a step's shape the launches depend on beyond the numbers of tokens, single-token entries and
+        portions: into how many tiles the tensor-core kernel cuts the portions (where they begin and how long each is,
+        the kernel reads on the device)."""
+        if self.variant != "tensor" or not ctx.n_prefill_segments:
             return ()
-        return ops.sigmoid_attention_tc_tiles(ctx.segments, self.group)
+        return (self.per_tile, ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile))
 
     def visible(self, position: int) -> int:
         first = 0
@@ -80,8 +83,10 @@ class PagedSigmoidAttention:
             return
         work_bytes, work_flops = self._work(ctx, q.element_size())
         if self.variant == "tensor" and rows is None:
-            ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, ctx, kv.block_table, out, self.nq, self.nkv, self.d,
-                                     self.dv, self.window, self.chunk, self.scale, self.head_bias, gate, gate_stride,
+            tiles = ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile) if ctx.n_prefill_segments else 0
+            ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles,
+                                     ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table, out, self.nq, self.nkv,
+                                     self.d, self.window, self.chunk, self.scale, self.head_bias, gate, gate_stride,
                                      error_flag=ctx.error_flag, work_bytes=work_bytes, work_flops=work_flops)
             return
         ops.sigmoid_attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, self.nq,
