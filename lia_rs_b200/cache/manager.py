@@ -9,7 +9,9 @@ pages per kind of need, and slots of fixed-size per-request state.
   the same page numbers (V with the values' head size where the need names one).  Different groups have pages of their own.
 * `ensure(slot, start, end)` makes the pages for positions [start, end) present in every group,
   all or nothing (src/inference/page_cache.rs:184-206).  In a window group the pages that lie
-  wholly before `start - window + 1` are given back first: no later token can see them.
+  wholly before `start - window + 1` are given back first: no later token can see them.  Likewise in a
+  group whose tokens read only their own block of `chunk` positions: the pages wholly before the block
+  of position `start`.
 * `release(slot)` gives everything back (request finished, aborted or preempted:
   src/server/paged/schedule.rs:134, preempt.rs:73,108).
 * Block tables live on the host and on the device; `flush()` copies the rows that changed.  The copies are
@@ -201,6 +203,9 @@ class CacheManager:
             raise_last()
         for group in self.groups:
             group._owner = self
+            chunk = getattr(group.request, "chunk", None)
+            if chunk and self._lib.lia_cache_set_chunk(self._handle, group.index, int(chunk)) < 0:
+                raise_last()
         self.group_of = {c: g for g in self.groups for c in g.cache_ids}
         self.states = {sid: torch.zeros((max_slots, *req.shape), dtype=req.dtype, device=device)
                        for sid, req in state_requests.items()}

@@ -68,6 +68,15 @@ LIA_HOST_EXPORT void* lia_cache_create(int n_groups, const int* num_pages, const
     return cache;
 }
 LIA_HOST_EXPORT void lia_cache_destroy(void* cache) { delete static_cast<Cache*>(cache); }
+// The tokens of group `group` read only keys of their own block of `chunk` positions (blocks counted from position 0;
+// 0: no such rule): pages that lie wholly before the block of a request's next token are given back.  Set before any
+// slot is admitted.
+LIA_HOST_EXPORT int lia_cache_set_chunk(void* handle, int group, int chunk) {
+    Cache* cache = static_cast<Cache*>(handle);
+    if (!cache || group < 0 || group >= (int)cache->groups.size() || chunk < 0) return refuse("no such group, or a negative chunk");
+    cache->groups[(size_t)group].chunk = chunk;
+    return 0;
+}
 
 LIA_HOST_EXPORT int lia_cache_available(void* handle, int group) { return static_cast<Cache*>(handle)->groups[(size_t)group].pool.available(); }
 

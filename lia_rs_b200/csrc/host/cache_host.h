@@ -69,6 +69,7 @@ struct Plan {
 struct Group {
     Pool pool;
     int page_size, window, max_slots, max_blocks;      // window < 0: all keys
+    int chunk = 0;                                     // > 0: a token reads only keys of its own block of `chunk` positions
     int32_t* host_table;                               // [max_slots, max_blocks], -1: no page
     std::vector<std::vector<int>> tables;              // per slot: page of each logical block, or -1
     std::vector<int> first_block;                      // blocks before this were given back
@@ -79,6 +80,15 @@ struct Group {
         : pool(pages), page_size(page_size_), window(window_), max_slots(slots), max_blocks(blocks), host_table(table),
           tables((size_t)slots), first_block((size_t)slots, 0), dirty_lo((size_t)slots, -1), dirty_hi((size_t)slots, 0) {}
 
+    bool keeps_all() const { return window < 0 && chunk <= 0; }
+    // The first block that a token at position `start` (and every later one) can still read: what lies wholly before
+    // its window, or before its block of `chunk` positions, is given back.
+    int first_block_kept(int start) const {
+        int first_key = 0;
+        if (window >= 0) first_key = std::max(first_key, start - window + 1);
+        if (chunk > 0) first_key = std::max(first_key, start / chunk * chunk);
+        return first_key / page_size;
+    }
     void mark(int slot, int lo, int hi) {
         if (dirty_lo[(size_t)slot] < 0) {
             dirty_lo[(size_t)slot] = lo;
@@ -95,8 +105,7 @@ struct Group {
     void needed(int slot, int start, int end, Plan* plan) const {
         const std::vector<int>& table = tables[(size_t)slot];
         const int n = (int)table.size(), first = first_block[(size_t)slot];
-        int keep_from = 0;
-        if (window >= 0) keep_from = std::max(0, start - window + 1) / page_size;
+        const int keep_from = first_block_kept(start);
         plan->allocate.clear();
         plan->give_back.clear();
         plan->keep_from = keep_from;
@@ -110,8 +119,7 @@ struct Group {
     void needed_by_scan(int slot, int start, int end, Plan* plan) const {
         const std::vector<int>& table = tables[(size_t)slot];
         const int n = (int)table.size();
-        int keep_from = 0;
-        if (window >= 0) keep_from = std::max(0, start - window + 1) / page_size;
+        const int keep_from = first_block_kept(start);
         plan->allocate.clear();
         plan->give_back.clear();
         plan->keep_from = keep_from;
@@ -186,7 +194,7 @@ struct Cache {
         int worst = 0;
         Plan plan;
         for (Group& group : groups) {
-            if (group.window < 0 && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size()) continue;
+            if (group.keeps_all() && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size()) continue;
             group.needed(slot, start, end, &plan);
             worst = std::max(worst, (int)plan.allocate.size() - (int)plan.give_back.size());
         }
@@ -200,7 +208,7 @@ struct Cache {
             return refuse("positions [" + std::to_string(start) + ", " + std::to_string(end) + ") are outside the context of " + std::to_string(max_context));
         bool present = true;
         for (const Group& group : groups)
-            present = present && group.window < 0 && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size();
+            present = present && group.keeps_all() && (end - 1) / group.page_size < (int)group.tables[(size_t)slot].size();
         if (!present) {                                  // (most decode steps find every position's page there)
             for (size_t g = 0; g < groups.size(); ++g) {
                 groups[g].needed(slot, start, end, &plans[g]);
