@@ -398,6 +398,70 @@ def other_workload(name, steps, warmup, trace=False) -> int:
     return 2
 
 
+# The Nafevik decoder beside the Llama decoder at equal sizes (--workload nafevik): widths, head counts, head sizes and
+# feed-forward sizes of the 2B- and 0.5B-class models, four layer runs each (Nafevik: one layer, then one layer run twice
+# with the re-injection ahead of each pass, then one layer), a vocabulary of 8,192, random weights.  For each model:
+# decode steps at batch 8 and 64 behind 2,048-token prompts, the 2,048-token prefill step, and every kernel class's share
+# of those steps with the fraction of its own roofline (bytes over the measured copy bandwidth for decode, flops over the
+# measured cuBLAS rate for prefill).
+NAFEVIK_SIZES = {
+    "2B-widths": dict(width=2048, heads=16, kv_heads=2, dim=128, ff=6144),
+    "0.5B-widths": dict(width=1024, heads=16, kv_heads=2, dim=64, ff=4096),
+}
+NAFEVIK_BLOCK = 1024          # positions per block of the attention
+
+
+def nafevik_pair(size: dict):
+    from lia_rs_b200 import LlamaConfig
+    from lia_rs_b200.config import NafevikConfig
+    mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
+             "scale": size["dim"] ** -0.5, "mask": {"size": NAFEVIK_BLOCK},
+             "rot": {"base": 10000.0, "dims": size["dim"], "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    layer = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    nafevik = NafevikConfig.from_dict({
+        "architecture": "Nafevik", "vocab": 8192, "width": size["width"], "max_positions": 4096, "norm": {"eps": 1e-5},
+        "residual_mult": 0.5, "canon": {"taps": 3}, "layers": [layer, layer, layer], "loop": {"start": 1, "stop": 2, "times": 2}})
+    llama = LlamaConfig.from_dict(dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=size["width"], intermediate_size=size["ff"],
+        num_hidden_layers=4, num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
+        vocab_size=8192, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096,
+        initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"))
+    return {"nafevik": nafevik, "llama": llama}
+
+
+def nafevik_workload(steps, warmup) -> int:
+    import torch
+    from lia_rs_b200.engine import Engine
+    peak = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    for name, size in NAFEVIK_SIZES.items():
+        sizes[name] = {}
+        for model, config in nafevik_pair(size).items():
+            batch = 64
+            pool = batch * (PROMPT + MAX_DECODE_STEPS + 64)
+            engine = Engine.random(config, seed=3, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=batch,
+                                   max_batch_tokens=PROMPT, max_context=4096)
+            point = {}
+            for b in (8, 64):
+                slots = fill(engine, b, PROMPT, 11 + b)
+                ms, launches, _, _ = time_decode(engine, slots, PROMPT, steps, warmup)
+                point[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(b / ms * 1e3, 1), "kernels": launches}
+                for slot in slots:
+                    engine.release(slot)
+            ms, drift = time_prefill(engine)
+            point["prefill_2048"] = {"ms": round(ms, 4), "tokens_per_s": round(PROMPT / ms * 1e3, 1), "graph_drift": drift}
+            point["kernels"] = kernel_shares(engine, 8, peak)
+            sizes[name][model] = point
+            del engine
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "nafevik", "metric": "Nafevik beside the Llama decoder at equal sizes, four layer runs, bf16",
+                      "data": "synthetic", "dtype": "bf16", "peaks": peak, "clocks": clocks, "sizes": sizes}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -408,7 +472,7 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
-    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed"],
+    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
     parser.add_argument("--device-trace", action="store_true",
                         help="with --workload 0.5b-mixed: one more pass under a trace of the device's kernels; adds "
@@ -427,6 +491,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "nafevik":
+        return nafevik_workload(args.steps, args.warmup)
     if args.workload:
         return other_workload(args.workload, args.steps, args.warmup, trace=args.device_trace)
 

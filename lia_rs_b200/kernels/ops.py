@@ -83,7 +83,7 @@ class _Signatures:
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                      c_void_p, c_int, c_int, c_void_p, c_void_p]
     lia_short_conv = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+                      c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p]
     lia_embedding_positions = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_float, c_void_p, c_void_p]
     lia_reinject_input = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
@@ -662,7 +662,8 @@ def short_conv(x, norm_weight, taps0, taps1, positions, slots, state, tail, out0
     with _timed("short_conv", nbytes=x.numel() * 4 + sum(o.numel() * o.element_size() for o in outs)):
         _check(lib().lia_short_conv(_p(x), _p(norm_weight), _p(taps0), _p(taps1), dtype_code(norm_weight.dtype),
                                     _p(positions), _p(slots), _p(state), _p(tail), _p(out0), _p(out1),
-                                    dtype_code(outs[0].dtype), n, width, taps, eps, 1 if single else 0, _stream()),
+                                    dtype_code(outs[0].dtype), n, width, taps, eps, 1 if single else 0,
+                                    _device_scratch(x.device)[1], _stream()),
                "short_conv")
 
 

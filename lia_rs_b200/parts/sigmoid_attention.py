@@ -82,7 +82,13 @@ class PagedSigmoidAttention:
         if rows is not None and n_rows == 0:
             return
         work_bytes, work_flops = self._work(ctx, q.element_size())
-        if self.variant == "tensor" and rows is None:
+        if self.variant == "tensor" and rows is not None:
+            # a few wanted rows (the last tokens of portions, in a model's last layer): each as a single token
+            ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, None, 0, 0, rows[:n_rows], ctx.positions, ctx.slots,
+                                     kv.block_table, out, self.nq, self.nkv, self.d, self.window, self.chunk, self.scale,
+                                     self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="rows")
+            return
+        if self.variant == "tensor":
             tiles = ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile) if ctx.n_prefill_segments else 0
             ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles,
                                      ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table, out, self.nq, self.nkv,

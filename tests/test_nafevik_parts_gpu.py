@@ -60,15 +60,16 @@ def test_embedding_with_learned_positions_and_reinjection_input():
         assert torch.equal(x, bias.float().expand(5, width))
 
 
+@pytest.mark.parametrize("width", [72, 70])           # 16-byte accesses, four channels a thread; and a width that does not allow them
 @pytest.mark.parametrize("taps", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_norm_and_short_convolution_with_carried_state(taps, dtype):
+def test_norm_and_short_convolution_with_carried_state(taps, dtype, width):
     """Three requests in three slots; their sequences come in steps of unequal runs (a run shorter than the taps, a
     run of one, single-token steps that move the state in the same kernel, rows of nobody).  Every output row equals
     the plain convolution of the whole sequence."""
     o = ops()
     g = torch.Generator().manual_seed(taps)
-    width, eps, slots = 72, 1e-5, 4
+    eps, slots = 1e-5, 4
     norm_w = (1 + 0.3 * torch.randn(width, generator=g)).to(torch.bfloat16)
     c = [(0.7 * torch.randn(width, taps, generator=g)).to(torch.bfloat16) for _ in range(2)]
     lengths = {0: 23, 2: 9, 3: 14}
@@ -115,6 +116,25 @@ def test_norm_and_short_convolution_with_carried_state(taps, dtype):
     o.short_conv(batch, norm_w.to(DEV), c[1].to(DEV), None, i32(range(6)), i32([1] * 6), state if taps > 1 else None,
                  torch.empty(6, width, device=DEV), alone, None, eps, False)
     close(alone, want[0][1][:6], dtype, "one reader")
+    # a long portion (eight rows a CTA, a token takes its earlier rows from the token ahead) behind a short one
+    g = torch.Generator().manual_seed(99)
+    long_x = torch.randn(1500, width, generator=g)
+    h = plain.rms_norm(long_x.double(), norm_w, eps)
+    want_long = [plain.input_conv(h, c[0]), plain.input_conv(h, c[1])]
+    got_long = [[], []]
+    at_long = 0
+    for count in (3, 1200, 1, 296):
+        batch = torch.cat([long_x[at_long:at_long + count], x[2][:5]]).to(DEV)          # another request's rows behind it
+        n = batch.shape[0]
+        out = [torch.empty(n, width, dtype=dtype, device=DEV) for _ in range(2)]
+        o.short_conv(batch, norm_w.to(DEV), c[0].to(DEV), c[1].to(DEV), i32(list(range(at_long, at_long + count)) + list(range(5))),
+                     i32([0] * count + [2] * 5), state if taps > 1 else None, torch.empty(n, width, device=DEV), out[0], out[1], eps, False)
+        for r in range(2):
+            got_long[r].append(out[r][:count])
+            close(out[r][count:], want[2][r][:5], dtype, f"the rows behind the long portion, reader {r}")
+        at_long += count
+    for r in range(2):
+        close(torch.cat(got_long[r]), want_long[r], dtype, f"long portions, reader {r}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
