@@ -91,19 +91,32 @@ short_conv_kernel(const float* __restrict__ x, const TW* __restrict__ norm_weigh
     // inverse root mean square of rows t0 - reach .. t0 + TOK - 1 (of the tile's own rows alone where every run is one
     // token): every thread adds its elements of a row, the warps' sums meet in a fixed order, so the order of the
     // additions depends on the width alone
-    for (int r = single ? reach : 0; r < TOK + reach; ++r) {
-        const int row = t0 - reach + r;
-        float sum = 0.f;
-        if (row >= 0 && row < n_tokens) {
-            const float* src = x + (size_t)row * width;
-            for (int i = threadIdx.x * V; i < width; i += THREADS * V) {
-                const Lanes<V> a = load_f32<V>(src + i);
+    // (the loads of all rows are asked for together: a row after the other would be a trip to memory each)
+    constexpr int NEEDED = TOK + CAP - 1;
+    {
+        float sums[NEEDED];
+        const float* rows[NEEDED];
 #pragma unroll
-                for (int e = 0; e < V; ++e) sum = fmaf(a.v[e], a.v[e], sum);
+        for (int r = 0; r < NEEDED; ++r) {
+            const int row = t0 - reach + r;
+            sums[r] = 0.f;
+            rows[r] = (r >= (single ? reach : 0) && r < TOK + reach && row >= 0 && row < n_tokens) ? x + (size_t)row * width : nullptr;
+        }
+        for (int i = threadIdx.x * V; i < width; i += THREADS * V) {
+#pragma unroll
+            for (int r = 0; r < NEEDED; ++r) {
+                if (rows[r]) {
+                    const Lanes<V> a = load_f32<V>(rows[r] + i);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) sums[r] = fmaf(a.v[e], a.v[e], sums[r]);
+                }
             }
         }
-        sum = warp_sum(sum);
-        if (lane == 0) partial[r][warp] = sum;
+#pragma unroll
+        for (int r = 0; r < NEEDED; ++r) {
+            const float sum = warp_sum(sums[r]);
+            if (lane == 0) partial[r][warp] = sum;
+        }
     }
     __syncthreads();
     if (threadIdx.x < TOK + reach) {
