@@ -20,7 +20,9 @@
 // What bounds a tile: two special-function instructions a weight (ex2, rcp): 32,768 per tile = 2,048 cycles of that
 // pipe, against 512 + 1,024 cycles of MMA at head size 128.
 //
-// Head sizes 64 and 128 (keys and values alike), g a divisor of 128; the caller uses the kernel for every size
+// Head sizes: multiples of 8 up to 128, keys and values each their own; in shared memory the rows of Q, K and V are
+// padded with zeros to D = 64 or 128 elements (what the swizzled tile and the MMA's K steps want), which costs the
+// padding's share of the tensor work and nothing else.  g a divisor of 128.  The caller uses the kernel for every size
 // (sigmoid_attention.cu) for everything else.
 #include "attention_tmem.cuh"
 
@@ -36,9 +38,9 @@ constexpr int STAGES = 3;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Params {
-    const __nv_bfloat16* q;          // [tokens, nq, D]
-    const __nv_bfloat16* k_pages;    // [pages, page_size, nkv, D]
-    const __nv_bfloat16* v_pages;
+    const __nv_bfloat16* q;          // [tokens, nq, d]
+    const __nv_bfloat16* k_pages;    // [pages, page_size, nkv, d]
+    const __nv_bfloat16* v_pages;    // [pages, page_size, nkv, dv]
     const int* segments;             // [n_segments][3]: first token's batch index, its position, count (portions of several tokens)
     const int* single_rows;          // [n_single]: batch indices of the single tokens
     const int* positions;            // [tokens]
@@ -46,8 +48,9 @@ struct Params {
     const int* block_table;          // [slots, table_stride]
     const float* head_bias;          // [nq] or null
     const float* gate;               // logits: token t, head h at gate[t * gate_stride + h]; or null
-    __nv_bfloat16* out;              // [tokens, nq, D]
+    __nv_bfloat16* out;              // [tokens, nq, dv]
     int n_segments, portion_tiles, n_single, gate_stride, table_stride, nq, nkv, page_size, page_shift, window, chunk, tokens_per_tile;
+    int d, dv;                       // the heads' real sizes (multiples of 8, at most D): rows are padded with zeros to D in shared memory
     float scale;
     int num_pages;
     int* error_flag;
@@ -143,8 +146,8 @@ sigmoid_attention_tc_kernel(Params p) {
         for (int id = lt; id < ROWS * PIECES; id += LOADERS) {
             const int r = id / PIECES, piece = id % PIECES;
             const int tok = r / group, head = r % group;
-            const bool valid = tok < tok_count;
-            const size_t src = ((size_t)(q_offset + tok0 + (valid ? tok : 0)) * p.nq + kvh * group + head) * D + piece * 8;
+            const bool valid = tok < tok_count && piece * 8 < p.d;
+            const size_t src = ((size_t)(q_offset + tok0 + (tok < tok_count ? tok : 0)) * p.nq + kvh * group + head) * p.d + (valid ? piece * 8 : 0);
             cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
         }
         cp_async_commit();                        // (Q is awaited below, with the first tile's copies already on their way)
@@ -170,8 +173,8 @@ sigmoid_attention_tc_kernel(Params p) {
 #pragma unroll
                 for (int i = 0; i < PASSES; ++i) {
                     const int row = __shfl_sync(0xffffffffu, my_row, lane_group + i);
-                    const bool valid = row >= 0;
-                    const size_t src = ((size_t)(valid ? row : 0) * p.nkv + kvh) * D + piece * 8;
+                    const bool valid = row >= 0 && piece * 8 < p.d;
+                    const size_t src = ((size_t)(row >= 0 ? row : 0) * p.nkv + kvh) * p.d + (valid ? piece * 8 : 0);
                     const uint32_t at = tile_offset<KT>(sub + i * ROWS_PER_PASS, piece);
                     cp_async_16(ks + at, p.k_pages + src, valid);
                     rows[i] = row;
@@ -180,8 +183,8 @@ sigmoid_attention_tc_kernel(Params p) {
                 if (j >= STAGES && !mbar_wait(smem_u32(&v_empty[st]), ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { ok = false; break; }
 #pragma unroll
                 for (int i = 0; i < PASSES; ++i) {
-                    const bool valid = rows[i] >= 0;
-                    const size_t src = ((size_t)(valid ? rows[i] : 0) * p.nkv + kvh) * D + piece * 8;
+                    const bool valid = rows[i] >= 0 && piece * 8 < p.dv;
+                    const size_t src = ((size_t)(rows[i] >= 0 ? rows[i] : 0) * p.nkv + kvh) * p.dv + (valid ? piece * 8 : 0);
                     cp_async_16(vs + tile_offset<KT>(sub + i * ROWS_PER_PASS, piece), p.v_pages + src, valid);
                 }
                 cp_async_commit();
@@ -299,7 +302,7 @@ sigmoid_attention_tc_kernel(Params p) {
             const int t = q_offset + tok0 + (row_ok ? tok : 0);
             float g = 1.0f;
             if (p.gate && row_ok) g = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.gate_stride + kvh * group + head]));
-            __nv_bfloat16* dst = p.out + ((size_t)t * p.nq + kvh * group + head) * D;
+            __nv_bfloat16* dst = p.out + ((size_t)t * p.nq + kvh * group + head) * p.dv;
 #pragma unroll 1
             for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
                 float o[16];
@@ -311,8 +314,8 @@ sigmoid_attention_tc_kernel(Params p) {
                         __nv_bfloat162 pair = __floats2bfloat162_rn(o[c] * g, o[c + 1] * g);
                         packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
                     }
-                    *reinterpret_cast<uint4*>(dst + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    if (c0 < p.dv) *reinterpret_cast<uint4*>(dst + c0) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    if (c0 + 8 < p.dv) *reinterpret_cast<uint4*>(dst + c0 + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
             }
         } else if (lane == 0 && p.error_flag) {
@@ -341,25 +344,25 @@ int launch(const Params& p, cudaStream_t stream) {
 }  // namespace
 
 // Tokens of a portion that one CTA takes for `group` query heads per kv head, key head size d and value head size dv
-// (0: this kernel does not take the combination; use lia_sigmoid_attention_generic).
+// (0: this kernel does not take the combination; use lia_sigmoid_attention_generic).  Head sizes: multiples of 8 up to 128.
 LIA_EXPORT int lia_sigmoid_attention_tc_tokens_per_tile(int group, int d, int dv) {
-    if (d != dv || (d != 64 && d != 128)) return 0;
+    if (d <= 0 || dv <= 0 || d % 8 || dv % 8 || d > 128 || dv > 128) return 0;
     return group >= 1 && group <= ROWS && ROWS % group == 0 ? ROWS / group : 0;
 }
 
-// q, out [tokens, nq, d] bfloat16; pages as lia_sigmoid_attention_generic (bfloat16, d == dv).  `segments`
+// q [tokens, nq, d], out [tokens, nq, dv] bfloat16; pages as lia_sigmoid_attention_generic (bfloat16).  `segments`
 // ([n_segments][3] int32: first batch index, first position, count) lists the portions of several tokens and
 // `portion_tiles` = sum over them of ceil(count / tokens_per_tile); `single_rows` lists the n_single batch indices of
 // single tokens, whose positions come from `positions`.  head_bias, gate, gate_stride, window, chunk: as there.
 LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                         int n_segments, int portion_tiles, const int* single_rows, int n_single,
                                         const int* positions, const int* slots, const int* block_table, int table_stride,
-                                        void* out, int nq, int nkv, int d, int page_size, int window, int chunk,
+                                        void* out, int nq, int nkv, int d, int dv, int page_size, int window, int chunk,
                                         float scale, const float* head_bias, const float* gate, int gate_stride,
                                         int num_pages, int* error_flag, cudaStream_t stream) {
     if (portion_tiles + n_single <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535 || portion_tiles < 0 || n_single < 0) return LIA_ERR_SIZE;
-    const int per_tile = lia_sigmoid_attention_tc_tokens_per_tile(nq / nkv, d, d);
+    const int per_tile = lia_sigmoid_attention_tc_tokens_per_tile(nq / nkv, d, dv);
     if (per_tile == 0) return LIA_ERR_SIZE;
     if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)k_pages & 15u) || ((uintptr_t)v_pages & 15u)) return LIA_ERR_ALIGN;
     Params p;
@@ -368,10 +371,10 @@ LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, cons
     p.head_bias = head_bias; p.gate = gate; p.out = (__nv_bfloat16*)out;
     p.n_segments = n_segments; p.portion_tiles = portion_tiles; p.n_single = n_single; p.gate_stride = gate_stride;
     p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.chunk = chunk;
-    p.tokens_per_tile = per_tile; p.scale = scale; p.num_pages = num_pages; p.error_flag = error_flag;
+    p.tokens_per_tile = per_tile; p.d = d; p.dv = dv; p.scale = scale; p.num_pages = num_pages; p.error_flag = error_flag;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;
-    if (d == 128) return launch<128>(p, stream);
+    if (d > 64 || dv > 64) return launch<128>(p, stream);        // rows padded with zeros to 128 elements, or to 64
     return launch<64>(p, stream);
 }

@@ -16,9 +16,9 @@ The four projections are one product against [Wq; Wk; Wv; Wg] (zero rows bring t
 Parameters: hidden, heads, kv_heads, head_dim, v_head_dim, scale, window, chunk, position (a PartSpec), and
 `names` (checkpoint names of q, k, v, o, gate and bias behind the part's prefix).
 
-`PagedSigmoidAttention` chooses the kernels: bfloat16 with head sizes that the tensor-core kernel is built for goes
-to csrc/sigmoid_attention_tc.cu (prompt portions and single tokens alike); everything else, and the whole 32-bit
-path, to the kernel for every size (csrc/sigmoid_attention.cu).
+`PagedSigmoidAttention` chooses the kernels: bfloat16 with head sizes that the tensor-core kernel takes (multiples of
+8 up to 128, a group that divides 128) goes to csrc/sigmoid_attention_tc.cu (prompt portions and single tokens alike);
+everything else, and the whole 32-bit path, to the kernel for every size (csrc/sigmoid_attention.cu).
 """
 from __future__ import annotations
 
@@ -85,14 +85,14 @@ class PagedSigmoidAttention:
         if self.variant == "tensor" and rows is not None:
             # a few wanted rows (the last tokens of portions, in a model's last layer): each as a single token
             ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, None, 0, 0, rows[:n_rows], ctx.positions, ctx.slots,
-                                     kv.block_table, out, self.nq, self.nkv, self.d, self.window, self.chunk, self.scale,
-                                     self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="rows")
+                                     kv.block_table, out, self.nq, self.nkv, self.d, self.dv, self.window, self.chunk,
+                                     self.scale, self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="rows")
             return
         if self.variant == "tensor":
             tiles = ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile) if ctx.n_prefill_segments else 0
             ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles,
                                      ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table, out, self.nq, self.nkv,
-                                     self.d, self.window, self.chunk, self.scale, self.head_bias, gate, gate_stride,
+                                     self.d, self.dv, self.window, self.chunk, self.scale, self.head_bias, gate, gate_stride,
                                      error_flag=ctx.error_flag, work_bytes=work_bytes, work_flops=work_flops)
             return
         ops.sigmoid_attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, self.nq,

@@ -272,19 +272,22 @@ def test_sigmoid_attention_one_key_decides(H, G, d, dv, chunk, window, page, dty
     assert int(flag.item()) == 0
 
 
-@pytest.mark.parametrize("H,G,d,chunk,window,page", [(4, 1, 64, 40, None, 16), (2, 2, 64, None, 37, 4), (8, 1, 128, 64, None, 16),
-                                                     (16, 2, 128, 130, 100, 8), (1, 1, 64, None, None, 16), (4, 4, 128, 300, None, 32)])
-def test_sigmoid_attention_on_the_tensor_cores(H, G, d, chunk, window, page):
-    """The tcgen05 kernel (bfloat16, head sizes 64 and 128) against the plain function and against the kernel for every
+@pytest.mark.parametrize("H,G,d,dv,chunk,window,page", [(4, 1, 64, 64, 40, None, 16), (2, 2, 64, 64, None, 37, 4), (8, 1, 128, 128, 64, None, 16),
+                                                        (16, 2, 128, 128, 130, 100, 8), (1, 1, 64, 64, None, None, 16), (4, 4, 128, 128, 300, None, 32),
+                                                        (4, 2, 40, 40, 50, None, 8), (8, 2, 96, 24, 120, None, 16), (2, 1, 16, 112, None, 60, 4),
+                                                        (4, 1, 72, 8, 33, None, 16)])
+def test_sigmoid_attention_on_the_tensor_cores(H, G, d, dv, chunk, window, page):
+    """The tcgen05 kernel (bfloat16, head sizes that are multiples of 8 up to 128, keys' and values' apart) against the plain function and against the kernel for every
     size: one portion of all tokens; two portions beside single tokens and a row of nobody; and the one-key probes
     at block, window and page edges as single decoded tokens."""
     o = ops()
     dtype = torch.bfloat16
-    assert o.sigmoid_attention_tc_accepts(H // G, d, d) and not o.sigmoid_attention_tc_accepts(H // G, d, d // 2)
-    per_tile = o.sigmoid_attention_tc_tokens_per_tile(H // G, d, d)
+    assert o.sigmoid_attention_tc_accepts(H // G, d, dv) and not o.sigmoid_attention_tc_accepts(H // G, d + 4, dv)
+    assert not o.sigmoid_attention_tc_accepts(H // G, 136, dv) and not o.sigmoid_attention_tc_accepts(3, d, dv)
+    per_tile = o.sigmoid_attention_tc_tokens_per_tile(H // G, d, dv)
     g = torch.Generator().manual_seed(H * 10 + d)
     T = 300
-    keys, values = torch.randn(T, G, d, generator=g), torch.randn(T, G, d, generator=g)
+    keys, values = torch.randn(T, G, d, generator=g), torch.randn(T, G, dv, generator=g)
     query = torch.randn(T, H, d, generator=g)
     gate = torch.randn(T, H, generator=g)
     bias = torch.rand(H, generator=g) * 3 - 2.5
@@ -300,27 +303,27 @@ def test_sigmoid_attention_on_the_tensor_cores(H, G, d, chunk, window, page):
     gate_dev = gate.contiguous().to(DEV)
 
     def run(portions, singles, slot_ids=slots):
-        out = torch.zeros(T, H * d, dtype=dtype, device=DEV)
+        out = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
         segments = i32([x for first, count in portions for x in (first, first, count)]).view(-1, 3) if portions else None
         tiles = sum((count + per_tile - 1) // per_tile for _, count in portions)
         o.sigmoid_attention_tc(q, k_pages, v_pages, segments, len(portions), tiles, i32(singles) if singles else None, positions,
-                               slot_ids, table, out, H, G, d, window, chunk, scale, bias.to(DEV), gate_dev, H, error_flag=flag)
+                               slot_ids, table, out, H, G, d, dv, window, chunk, scale, bias.to(DEV), gate_dev, H, error_flag=flag)
         return out
 
     whole = run([(0, T)], [])
-    close(whole.view(T, H, d), want, dtype, "one portion")
-    generic = torch.zeros(T, H * d, dtype=dtype, device=DEV)
-    o.sigmoid_attention_generic(q, k_pages, v_pages, positions, slots, table, generic, H, G, d, d, window, chunk, scale, bias.to(DEV),
+    close(whole.view(T, H, dv), want, dtype, "one portion")
+    generic = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
+    o.sigmoid_attention_generic(q, k_pages, v_pages, positions, slots, table, generic, H, G, d, dv, window, chunk, scale, bias.to(DEV),
                                 gate_dev, H, error_flag=flag)
     close(whole, generic.double().cpu(), dtype, "against the kernel for every size")
     nobody = slots.clone()
     nobody[7] = -1
     mixed = run([(10, 140), (150, 149)], [0, 5, 9, 299, 7], nobody)
     rows = [0, 5, 9] + list(range(10, 300))
-    close(mixed[rows].view(len(rows), H, d), want[rows], dtype, "portions beside single tokens")
+    close(mixed[rows].view(len(rows), H, dv), want[rows], dtype, "portions beside single tokens")
     assert float(mixed[7].abs().max()) == 0.0 and float(mixed[6].abs().max()) == 0.0       # nobody's row and an absent row
     one_by_one = run([], list(range(0, T, 7)))
-    close(one_by_one[::7].view(-1, H, d), want[::7], dtype, "single tokens")
+    close(one_by_one[::7].view(-1, H, dv), want[::7], dtype, "single tokens")
     # one key decides
     low = torch.full((H,), -14.0)
     for p in (1, 129, 255, 299):
@@ -337,12 +340,12 @@ def test_sigmoid_attention_on_the_tensor_cores(H, G, d, chunk, window, page):
             kp, vp, _ = _paged(probe_keys, values, page, pages, order, dtype)
             qq = torch.zeros(T, H, d)
             qq[p] = probe.repeat_interleave(H // G, dim=0)
-            out = torch.zeros(T, H * d, dtype=dtype, device=DEV)
+            out = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
             o.sigmoid_attention_tc(qq.view(T, H * d).to(dtype).to(DEV), kp, vp, None, 0, 0, i32([p]), positions, slots, table, out, H, G,
-                                   d, window, chunk, scale, low.to(DEV), gate_dev, H, error_flag=flag)
-            got = out[p].view(H, d).float().cpu()
+                                   d, dv, window, chunk, scale, low.to(DEV), gate_dev, H, error_flag=flag)
+            got = out[p].view(H, dv).float().cpu()
             for h in range(H):
-                expect = values[j, h // (H // G)] * torch.sigmoid(gate[p, h]) if seen else torch.zeros(d)
+                expect = values[j, h // (H // G)] * torch.sigmoid(gate[p, h]) if seen else torch.zeros(dv)
                 assert float((got[h] - expect).abs().max()) <= 0.03 * max(1.0, float(expect.abs().max())), (p, j, seen, h)
     torch.cuda.synchronize()
     assert int(flag.item()) == 0
