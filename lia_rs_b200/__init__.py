@@ -1,12 +1,12 @@
 """lia_rs_b200: a small, whole inference engine for one B200, for the MiniCPM5 Llama
-architecture of Heltion/lia.rs: configuration and registry, safetensors weights, layers built
+architecture of Heltion/lia.rs (and, from parts registered beside it, the Nafevik decoder): configuration and registry, safetensors weights, layers built
 from parts, a paged cache manager, one step function, a scheduler, sampling, a command line and
 `generate()`; every forward operation is a hand-written sm_100a CUDA kernel."""
 from . import models as _models  # noqa: F401  (registers the built-in architecture)
-from .config import ConfigError, LlamaConfig, register_architecture, resolve_architecture
+from .config import ConfigError, LlamaConfig, NafevikConfig, register_architecture, resolve_architecture
 from .weights import WeightError, write_random_model
 
-__all__ = ["ConfigError", "LlamaConfig", "register_architecture", "resolve_architecture", "WeightError",
+__all__ = ["ConfigError", "LlamaConfig", "NafevikConfig", "register_architecture", "resolve_architecture", "WeightError",
            "write_random_model", "Engine", "StepEntry", "generate", "replay", "Sampling"]
 
 

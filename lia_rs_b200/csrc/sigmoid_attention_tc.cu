@@ -1,7 +1,7 @@
 // Attention with sigmoid weights (no softmax, no normalisation; see sigmoid_attention.cu for the definition) over the
 // paged bfloat16 cache on the 5th-generation tensor cores, for prompt portions and single decoded tokens alike.
 //
-// A CTA owns 128 query rows = (128 / g) consecutive tokens x the g query heads of one kv head (a single decoded token
+// A CTA owns up to 128 query rows = floor(128 / g) consecutive tokens x the g query heads of one kv head (a single decoded token
 // is a portion of one token), and walks the keys its rows can see, 128 at a time, from the first key that the
 // CTA's first token sees (the start of its block of `chunk` positions, or of its window) to its last token:
 //     S = Q K^T      tcgen05.mma, M 128 (rows), N 128 (keys), K head_dim, accumulator in TMEM (two buffers)
@@ -22,7 +22,7 @@
 //
 // Head sizes: multiples of 8 up to 128, keys and values each their own; in shared memory the rows of Q, K and V are
 // padded with zeros to D = 64 or 128 elements (what the swizzled tile and the MMA's K steps want), which costs the
-// padding's share of the tensor work and nothing else.  g a divisor of 128.  The caller uses the kernel for every size
+// padding's share of the tensor work and nothing else.  Any g up to 128 (rows beyond (128 / g) g stay idle).  The caller uses the kernel for every size
 // (sigmoid_attention.cu) for everything else.
 #include "attention_tmem.cuh"
 
@@ -54,7 +54,49 @@ struct Params {
     float scale;
     int num_pages;
     int* error_flag;
+    // A step of single tokens may leave the position encoding and the append to this kernel: `fused_rows` (32-bit, a row
+    // of `fused_stride` floats a token: nq heads of d queries, nkv heads of d keys, nkv heads of dv values, as the
+    // product before left them) replaces q; each CTA encodes its token's queries and key (rotary over adjacent pairs of
+    // the first rotary_dim elements, frequencies `freq`, sine and cosine times `magnitude`), puts them into its tiles
+    // and, with `write_kv`, the key and value into their page.
+    const float* fused_rows;
+    const float* freq;
+    int fused_stride, rotary_dim, write_kv;
+    float magnitude;
 };
+
+// Eight consecutive elements (from e0, a multiple of 8) of a head's 32-bit row, rotary-encoded where they lie within
+// rotary_dim, as four bfloat16 pairs.  The arithmetic is that of rotary_pairs.cu.
+__device__ __forceinline__ uint4 encoded_piece(const float* head, int e0, int pos, const float* freq, int rotary_dim, float magnitude) {
+    const float4 lo = *reinterpret_cast<const float4*>(head + e0), hi = *reinterpret_cast<const float4*>(head + e0 + 4);
+    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = e0 + 2 * i;
+        if (e < rotary_dim) {
+            float sn, cs;
+            sincosf((float)pos * freq[e >> 1], &sn, &cs);
+            cs *= magnitude;
+            sn *= magnitude;
+            const float a = v[2 * i], b = v[2 * i + 1];
+            v[2 * i] = a * cs - b * sn;
+            v[2 * i + 1] = b * cs + a * sn;
+        }
+    }
+    uint4 out;
+    __nv_bfloat162 pair = __floats2bfloat162_rn(v[0], v[1]);
+    out.x = *reinterpret_cast<uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(v[2], v[3]);
+    out.y = *reinterpret_cast<uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(v[4], v[5]);
+    out.z = *reinterpret_cast<uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(v[6], v[7]);
+    out.w = *reinterpret_cast<uint32_t*>(&pair);
+    return out;
+}
+__device__ __forceinline__ void store_shared_16(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 
 __device__ __forceinline__ float rcp_approx(float x) {
     float y;
@@ -147,11 +189,22 @@ sigmoid_attention_tc_kernel(Params p) {
             const int r = id / PIECES, piece = id % PIECES;
             const int tok = r / group, head = r % group;
             const bool valid = tok < tok_count && piece * 8 < p.d;
+            if (p.fused_rows) {
+                // the token's queries from the product's 32-bit row, encoded here (rows beyond its heads are zeros)
+                uint4 piece_bits = make_uint4(0u, 0u, 0u, 0u);
+                if (valid)
+                    piece_bits = encoded_piece(p.fused_rows + (size_t)q_offset * p.fused_stride + (size_t)(kvh * group + head) * p.d, piece * 8,
+                                               seg_start, p.freq, p.rotary_dim, p.magnitude);
+                store_shared_16(q_s + tile_offset<ROWS>(r, piece), piece_bits);
+                continue;
+            }
             const size_t src = ((size_t)(q_offset + tok0 + (tok < tok_count ? tok : 0)) * p.nq + kvh * group + head) * p.d + (valid ? piece * 8 : 0);
             cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
         }
         cp_async_commit();                        // (Q is awaited below, with the first tile's copies already on their way)
         bool ok = true;
+        int own_row = -1, own_piece = 0;              // fused step: the page row of the token's own key, if this thread holds a piece of it
+        uint32_t own_at = 0;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j % STAGES;
             // the keys' stage is free as soon as the first product of three tiles ago has read it, the values' stage
@@ -166,6 +219,7 @@ sigmoid_attention_tc_kernel(Params p) {
                 static_assert(PASSES <= PIECES, "one lane per pass");
                 const int sub = lt / PIECES, piece = lt % PIECES, lane_group = (lane / PIECES) * PIECES;
                 int my_row = -1, rows[PASSES];
+                int own = -1;                          // the pass whose row is the token's own key (encoded here, not read)
                 if (piece < PASSES) {
                     const int key = key0 + sub + piece * ROWS_PER_PASS;
                     if (key < key_end) my_row = cache_row_of(table, key, p.page_size, p.page_shift, p.num_pages, p.error_flag);
@@ -173,7 +227,9 @@ sigmoid_attention_tc_kernel(Params p) {
 #pragma unroll
                 for (int i = 0; i < PASSES; ++i) {
                     const int row = __shfl_sync(0xffffffffu, my_row, lane_group + i);
-                    const bool valid = row >= 0 && piece * 8 < p.d;
+                    const bool mine = p.fused_rows && key0 + sub + i * ROWS_PER_PASS == pos_last;
+                    if (mine) own = i;
+                    const bool valid = row >= 0 && piece * 8 < p.d && !mine;
                     const size_t src = ((size_t)(row >= 0 ? row : 0) * p.nkv + kvh) * p.d + (valid ? piece * 8 : 0);
                     const uint32_t at = tile_offset<KT>(sub + i * ROWS_PER_PASS, piece);
                     cp_async_16(ks + at, p.k_pages + src, valid);
@@ -183,11 +239,16 @@ sigmoid_attention_tc_kernel(Params p) {
                 if (j >= STAGES && !mbar_wait(smem_u32(&v_empty[st]), ((uint32_t)(j / STAGES) & 1u) ^ 1u)) { ok = false; break; }
 #pragma unroll
                 for (int i = 0; i < PASSES; ++i) {
-                    const bool valid = rows[i] >= 0 && piece * 8 < p.dv;
+                    const bool valid = rows[i] >= 0 && piece * 8 < p.dv && i != own;
                     const size_t src = ((size_t)(rows[i] >= 0 ? rows[i] : 0) * p.nkv + kvh) * p.dv + (valid ? piece * 8 : 0);
                     cp_async_16(vs + tile_offset<KT>(sub + i * ROWS_PER_PASS, piece), p.v_pages + src, valid);
                 }
                 cp_async_commit();
+                own_row = -1;
+#pragma unroll
+                for (int i = 0; i < PASSES; ++i)
+                    if (i == own) { own_row = rows[i]; own_at = tile_offset<KT>(sub + i * ROWS_PER_PASS, piece); }
+                own_piece = piece;
             }
             if (j == 0) {
                 asm volatile("cp.async.wait_group 2;" ::: "memory");    // Q has landed (groups complete in the order they were made)
@@ -195,9 +256,21 @@ sigmoid_attention_tc_kernel(Params p) {
                 mbar_arrive(smem_u32(&q_full));
             }
             asm volatile("cp.async.wait_group 1;" ::: "memory");        // the keys have landed
+            const float* fused = p.fused_rows ? p.fused_rows + (size_t)q_offset * p.fused_stride : nullptr;
+            if (own_row >= 0 && own_piece * 8 < p.d) {
+                // the token's own key: encoded, into the tile (over the zeros its copy left) and into its page
+                const uint4 bits = encoded_piece(fused + (size_t)(p.nq + kvh) * p.d, own_piece * 8, pos_last, p.freq, p.rotary_dim, p.magnitude);
+                store_shared_16(ks + own_at, bits);
+                if (p.write_kv) *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(p.k_pages) + ((size_t)own_row * p.nkv + kvh) * p.d + own_piece * 8) = bits;
+            }
             fence_async_smem();
             mbar_arrive(smem_u32(&k_full[st]));
             cp_async_wait_all();
+            if (own_row >= 0 && own_piece * 8 < p.dv) {
+                const uint4 bits = encoded_piece(fused + (size_t)(p.nq + p.nkv) * p.d + (size_t)kvh * p.dv, own_piece * 8, pos_last, p.freq, 0, 1.0f);
+                store_shared_16(vs + own_at, bits);
+                if (p.write_kv) *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(p.v_pages) + ((size_t)own_row * p.nkv + kvh) * p.dv + own_piece * 8) = bits;
+            }
             fence_async_smem();
             mbar_arrive(smem_u32(&v_full[st]));
         }
@@ -347,20 +420,25 @@ int launch(const Params& p, cudaStream_t stream) {
 // (0: this kernel does not take the combination; use lia_sigmoid_attention_generic).  Head sizes: multiples of 8 up to 128.
 LIA_EXPORT int lia_sigmoid_attention_tc_tokens_per_tile(int group, int d, int dv) {
     if (d <= 0 || dv <= 0 || d % 8 || dv % 8 || d > 128 || dv > 128) return 0;
-    return group >= 1 && group <= ROWS && ROWS % group == 0 ? ROWS / group : 0;
+    return group >= 1 && group <= ROWS ? ROWS / group : 0;       // a group that does not divide 128 leaves the last rows idle
 }
 
 // q [tokens, nq, d], out [tokens, nq, dv] bfloat16; pages as lia_sigmoid_attention_generic (bfloat16).  `segments`
 // ([n_segments][3] int32: first batch index, first position, count) lists the portions of several tokens and
 // `portion_tiles` = sum over them of ceil(count / tokens_per_tile); `single_rows` lists the n_single batch indices of
 // single tokens, whose positions come from `positions`.  head_bias, gate, gate_stride, window, chunk: as there.
+// `fused_rows` (optional, only for a step without portions): see Params; q is then not read.
 LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                         int n_segments, int portion_tiles, const int* single_rows, int n_single,
                                         const int* positions, const int* slots, const int* block_table, int table_stride,
                                         void* out, int nq, int nkv, int d, int dv, int page_size, int window, int chunk,
                                         float scale, const float* head_bias, const float* gate, int gate_stride,
-                                        int num_pages, int* error_flag, cudaStream_t stream) {
+                                        int num_pages, const float* fused_rows, int fused_stride, const float* freq,
+                                        int rotary_dim, float magnitude, int write_kv, int* error_flag, cudaStream_t stream) {
     if (portion_tiles + n_single <= 0) return LIA_OK;
+    if (fused_rows && (portion_tiles > 0 || fused_stride < (nq + nkv) * d + nkv * dv || fused_stride % 4 || ((uintptr_t)fused_rows & 15u) ||
+                       rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim > 0 && !freq)))
+        return LIA_ERR_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535 || portion_tiles < 0 || n_single < 0) return LIA_ERR_SIZE;
     const int per_tile = lia_sigmoid_attention_tc_tokens_per_tile(nq / nkv, d, dv);
     if (per_tile == 0) return LIA_ERR_SIZE;
@@ -372,6 +450,8 @@ LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, cons
     p.n_segments = n_segments; p.portion_tiles = portion_tiles; p.n_single = n_single; p.gate_stride = gate_stride;
     p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.chunk = chunk;
     p.tokens_per_tile = per_tile; p.d = d; p.dv = dv; p.scale = scale; p.num_pages = num_pages; p.error_flag = error_flag;
+    p.fused_rows = fused_rows; p.fused_stride = fused_stride; p.freq = freq; p.rotary_dim = rotary_dim; p.magnitude = magnitude;
+    p.write_kv = write_kv;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -90,7 +90,7 @@ class _Signatures:
     lia_sigmoid_attention_tc_tokens_per_tile = [c_int, c_int, c_int]
     lia_sigmoid_attention_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                c_void_p, c_int, c_int, c_void_p, c_void_p]
+                                c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p]
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -717,7 +717,7 @@ def sigmoid_attention_tc_tokens_per_tile(group: int, d: int, dv: int) -> int:
 
 def sigmoid_attention_tc_accepts(group: int, d: int, dv: int) -> bool:
     """Whether the tensor-core kernel for sigmoid attention takes these sizes (bfloat16): head sizes of keys and of
-    values that are multiples of 8 up to 128, and a number of query heads per kv head that divides 128."""
+    values that are multiples of 8 up to 128, and at most 128 query heads per kv head."""
     return sigmoid_attention_tc_tokens_per_tile(group, d, dv) > 0
 
 
@@ -728,24 +728,36 @@ def sigmoid_attention_tc_tiles(segments, per_tile: int) -> int:
 
 def sigmoid_attention_tc(q, k_pages, v_pages, segments, n_segments, portion_tiles, single_rows, positions, slots,
                          block_table, out, nq, nkv, d, dv, window, chunk, scale, head_bias=None, gate=None, gate_stride=0,
-                         error_flag=None, label=None, work_bytes=0, work_flops=0):
+                         error_flag=None, label=None, work_bytes=0, work_flops=0, fused_rows=None, freq=None, rotary_dim=0,
+                         magnitude=1.0, write_kv=True):
     """Sigmoid attention on the tcgen05 tensor cores (bfloat16) for the portions listed in `segments` ([n_segments, 3]
     int32: first batch index, first position, count) and the single tokens whose batch indices `single_rows` lists;
-    see csrc/sigmoid_attention_tc.cu."""
-    _cuda(q, k_pages, v_pages, segments, single_rows, positions, slots, block_table, out, head_bias, error_flag)
-    if not (q.dtype == k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16):
+    see csrc/sigmoid_attention_tc.cu.  With `fused_rows` (a step of single tokens only: the 32-bit rows of q, k and v
+    heads that the product before left, `q` may be None) the kernel applies the pairwise rotary encoding (`freq`,
+    `rotary_dim`, `magnitude`) to the queries and the key itself and, with `write_kv`, appends key and value to the pages:
+    no position-encoding kernel runs."""
+    _cuda(q, k_pages, v_pages, segments, single_rows, positions, slots, block_table, out, head_bias, error_flag, freq)
+    if not (k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16) or (q is not None and q.dtype != torch.bfloat16):
         raise KernelError("sigmoid_attention_tc is a bfloat16 kernel")
-    if tuple(k_pages.shape[2:]) != (nkv, d) or tuple(v_pages.shape[2:]) != (nkv, dv) or q.shape[1] != nq * d or out.shape[1] != nq * dv:
+    if tuple(k_pages.shape[2:]) != (nkv, d) or tuple(v_pages.shape[2:]) != (nkv, dv) or out.shape[1] != nq * dv or \
+            (q is not None and q.shape[1] != nq * d):
         raise KernelError("sigmoid_attention_tc: q, out and the pages do not have the heads' sizes")
     if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != nq):
         raise KernelError("sigmoid attention: head_bias must be 32-bit, one per query head")
     if gate is not None and (gate.dtype != torch.float32 or not gate.is_cuda):
         raise KernelError("sigmoid attention: gate logits must be 32-bit")
+    if fused_rows is None and q is None:
+        raise KernelError("sigmoid_attention_tc needs q or the rows to encode")
+    if fused_rows is not None and (fused_rows.dtype != torch.float32 or not fused_rows.is_cuda or fused_rows.stride(1) != 1
+                                   or (freq is not None and freq.dtype != torch.float32)):
+        raise KernelError("sigmoid_attention_tc: the rows to encode and the frequencies must be 32-bit")
     n_single = 0 if single_rows is None else single_rows.numel()
     with _timed("sigmoid_attention_tc", label, work_bytes, work_flops):
         _check(lib().lia_sigmoid_attention_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), int(n_segments),
                                               int(portion_tiles), _p(single_rows), n_single, _p(positions), _p(slots),
                                               _p(block_table), block_table.shape[1], _p(out), nq, nkv, d, dv,
                                               k_pages.shape[1], int(window or 0), int(chunk or 0), scale, _p(head_bias),
-                                              _p(gate), int(gate_stride), k_pages.shape[0], _p(error_flag), _stream()),
+                                              _p(gate), int(gate_stride), k_pages.shape[0], _p(fused_rows),
+                                              0 if fused_rows is None else fused_rows.stride(0), _p(freq), int(rotary_dim),
+                                              float(magnitude), 1 if write_kv else 0, _p(error_flag), _stream()),
                "sigmoid_attention_tc")

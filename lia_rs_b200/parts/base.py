@@ -154,6 +154,13 @@ class PositionEncoding(Part):
         None and runs its own `encode_and_store` ahead of the attention kernel, at every step."""
         return None
 
+    def pairs_record(self):
+        """`(rotary_dim, frequencies, magnitude)` if this encoding is exactly "rotate the adjacent pairs (2i, 2i+1) of the
+        first rotary_dim elements of every q and k head by position * frequencies[i], sine and cosine times magnitude"
+        (rotary_dim 0: nothing is encoded), else None.  An attention kernel that can apply such an encoding itself,
+        with the append to the cache, then needs no `encode_and_store` in steps of single tokens."""
+        return None
+
 
 class Mixer(Part):
     # True: `forward` takes `rows` / `n_rows` (only those tokens' outputs are needed, `residual` holds those rows

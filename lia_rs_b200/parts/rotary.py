@@ -111,6 +111,10 @@ class RotaryPairs(PositionEncoding):
             freq, self.magnitude = scaled_frequencies(params["base"], self.rotary_dim, params.get("scaling"))
             self.freq = freq.to(torch.float32).to(runtime.device)
 
+    def pairs_record(self):
+        """(rotary_dim, frequencies, magnitude): all a kernel needs to apply this encoding itself."""
+        return self.rotary_dim, self.freq, self.magnitude
+
     def encode_and_store(self, ctx, qkv, q_out, kv, nq, nkv, d, v_dim=None):
         self.runtime.ops.rotary_pairs_kv_write(qkv, ctx.positions, ctx.slots, kv.block_table, q_out, kv.k_pages,
                                                kv.v_pages, nq, nkv, d, d if v_dim is None else v_dim, self.rotary_dim,

@@ -17,7 +17,7 @@ Parameters: hidden, heads, kv_heads, head_dim, v_head_dim, scale, window, chunk,
 `names` (checkpoint names of q, k, v, o, gate and bias behind the part's prefix).
 
 `PagedSigmoidAttention` chooses the kernels: bfloat16 with head sizes that the tensor-core kernel takes (multiples of
-8 up to 128, a group that divides 128) goes to csrc/sigmoid_attention_tc.cu (prompt portions and single tokens alike);
+8 up to 128) goes to csrc/sigmoid_attention_tc.cu (prompt portions and single tokens alike);
 everything else, and the whole 32-bit path, to the kernel for every size (csrc/sigmoid_attention.cu).
 """
 from __future__ import annotations
@@ -75,6 +75,22 @@ class PagedSigmoidAttention:
         keys = sum(self.visible(start) for _, start, count, _ in ctx.segments if count == 1)
         pairs = sum(self.visible(start + i) for _, start, count, _ in ctx.segments if count > 1 for i in range(count))
         return keys * self.nkv * (self.d + self.dv) * element_size, 2 * self.nq * (self.d + self.dv) * pairs
+
+    def forward_fused(self, ctx, projected, kv, out, pairs, gate=None, gate_stride=0) -> bool:
+        """For a step of single decoded tokens, the tensor-core variant and a pairwise rotary (or no) encoding
+        (`pairs`: what the encoding answers to `pairs_record()`): encoding of q and k, append of k and v to `kv`, and
+        attention in one kernel, from the product's 32-bit rows `projected`.  Returns False, having done nothing, when
+        the step or this attention is not of that kind; the caller then encodes and attends separately."""
+        if self.variant != "tensor" or pairs is None or not ctx.decode_only or kv.k_pages.dtype != torch.bfloat16:
+            return False
+        rotary_dim, freq, magnitude = pairs
+        work_bytes, _ = self._work(ctx, 2)
+        ops.sigmoid_attention_tc(None, kv.k_pages, kv.v_pages, None, 0, 0, ctx.decode_rows, ctx.positions, ctx.slots,
+                                 kv.block_table, out, self.nq, self.nkv, self.d, self.dv, self.window, self.chunk, self.scale,
+                                 self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="fused",
+                                 work_bytes=work_bytes, fused_rows=projected, freq=freq, rotary_dim=rotary_dim,
+                                 magnitude=magnitude, write_kv=kv.writes)
+        return True
 
     def forward(self, ctx, q, kv, out, gate=None, gate_stride=0, rows=None, n_rows=None):
         """out[t] = gated attention of token t's encoded queries over `kv` (this step's keys and values already
@@ -167,10 +183,14 @@ class SigmoidAttention(Mixer):
         flag = ctx.error_flag
         projected = ctx.buffer("sattn.in", (n, self.width), torch.float32)
         linear(rt, STORE, x, self.w_in, projected, error_flag=flag, name="qkvg")
-        q = ctx.buffer("sattn.q", (n, nq * d), rt.compute_dtype)
-        self.position.encode_and_store(ctx, projected, q, kv, nq, nkv, d, v_dim=dv)
         o = ctx.buffer("sattn.o", (n, nq * dv), rt.compute_dtype)
         gate = projected[:, self.gate_offset:]
+        if rows is None and self.attention.forward_fused(ctx, projected, kv, o, self.position.pairs_record(), gate=gate,
+                                                         gate_stride=self.width):
+            linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+            return
+        q = ctx.buffer("sattn.q", (n, nq * d), rt.compute_dtype)
+        self.position.encode_and_store(ctx, projected, q, kv, nq, nkv, d, v_dim=dv)
         if rows is None:
             self.attention.forward(ctx, q, kv, o, gate=gate, gate_stride=self.width)
             linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

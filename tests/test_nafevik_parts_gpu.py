@@ -275,7 +275,8 @@ def test_sigmoid_attention_one_key_decides(H, G, d, dv, chunk, window, page, dty
 @pytest.mark.parametrize("H,G,d,dv,chunk,window,page", [(4, 1, 64, 64, 40, None, 16), (2, 2, 64, 64, None, 37, 4), (8, 1, 128, 128, 64, None, 16),
                                                         (16, 2, 128, 128, 130, 100, 8), (1, 1, 64, 64, None, None, 16), (4, 4, 128, 128, 300, None, 32),
                                                         (4, 2, 40, 40, 50, None, 8), (8, 2, 96, 24, 120, None, 16), (2, 1, 16, 112, None, 60, 4),
-                                                        (4, 1, 72, 8, 33, None, 16)])
+                                                        (4, 1, 72, 8, 33, None, 16), (3, 1, 32, 16, 7, None, 4), (10, 2, 64, 64, 90, None, 16),
+                                                        (7, 7, 48, 48, None, None, 8)])
 def test_sigmoid_attention_on_the_tensor_cores(H, G, d, dv, chunk, window, page):
     """The tcgen05 kernel (bfloat16, head sizes that are multiples of 8 up to 128, keys' and values' apart) against the plain function and against the kernel for every
     size: one portion of all tokens; two portions beside single tokens and a row of nobody; and the one-key probes
@@ -283,7 +284,7 @@ def test_sigmoid_attention_on_the_tensor_cores(H, G, d, dv, chunk, window, page)
     o = ops()
     dtype = torch.bfloat16
     assert o.sigmoid_attention_tc_accepts(H // G, d, dv) and not o.sigmoid_attention_tc_accepts(H // G, d + 4, dv)
-    assert not o.sigmoid_attention_tc_accepts(H // G, 136, dv) and not o.sigmoid_attention_tc_accepts(3, d, dv)
+    assert not o.sigmoid_attention_tc_accepts(H // G, 136, dv)
     per_tile = o.sigmoid_attention_tc_tokens_per_tile(H // G, d, dv)
     g = torch.Generator().manual_seed(H * 10 + d)
     T = 300
@@ -349,3 +350,61 @@ def test_sigmoid_attention_on_the_tensor_cores(H, G, d, dv, chunk, window, page)
                 assert float((got[h] - expect).abs().max()) <= 0.03 * max(1.0, float(expect.abs().max())), (p, j, seen, h)
     torch.cuda.synchronize()
     assert int(flag.item()) == 0
+
+
+@pytest.mark.parametrize("H,G,d,dv,dims,chunk,page", [(4, 2, 64, 64, 64, 40, 16), (8, 1, 128, 128, 32, None, 8), (4, 1, 48, 24, 48, 120, 16),
+                                                      (3, 3, 16, 40, 0, 7, 4)])
+def test_single_tokens_encoded_and_appended_inside_the_attention_kernel(H, G, d, dv, dims, chunk, page):
+    """A step of single tokens through the one kernel that encodes q and k, appends k and v and attends, against the
+    encoding kernel followed by the attention kernel: the same outputs and the same pages (to 16-bit rounding: the two
+    may contract their multiplications differently), the other pages untouched, a row of nobody skipped."""
+    from lia_rs_b200.parts.rotary import scaled_frequencies
+    o = ops()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(d + dv)
+    contexts = [0, 1, 39, 40, 130, 255, 77]                        # each token's position: its request holds that many keys
+    slot_ids = [0, 1, 2, 3, 4, 5, -1]
+    n, slots = len(contexts), 6
+    blocks = 256 // page + 1
+    pages = slots * blocks + 2
+    order = torch.randperm(pages, generator=g).tolist()
+    table = torch.full((slots, blocks), -1, dtype=torch.int32)
+    k_pages = torch.zeros(pages, page, G, d)
+    v_pages = torch.zeros(pages, page, G, dv)
+    for s in range(slots):
+        for b in range(contexts[s] // page + 1):
+            table[s, b] = order[s * blocks + b]
+            held = min(page, contexts[s] - b * page)               # keys of earlier steps in this page
+            if held > 0:
+                k_pages[table[s, b], :held] = torch.randn(held, G, d, generator=g)
+                v_pages[table[s, b], :held] = torch.randn(held, G, dv, generator=g)
+    width = ((H + G) * d + G * dv + H + 7) // 8 * 8
+    rows = torch.randn(n, width, generator=g).to(DEV)
+    gate_offset = (H + G) * d + G * dv
+    freq, magnitude = (scaled_frequencies(700.0, dims, {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}) if dims else (None, 1.0))
+    freq = None if freq is None else freq.float().to(DEV)
+    bias = (torch.rand(H, generator=g) * 2 - 2).to(DEV)
+    positions, slot_dev, table = i32(contexts), i32(slot_ids), table.to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    singles = i32(range(n))
+    # apart: the encoding kernel, then the attention kernel
+    ka, va = k_pages.to(dtype).to(DEV), v_pages.to(dtype).to(DEV)
+    q = torch.zeros(n, H * d, dtype=dtype, device=DEV)
+    o.rotary_pairs_kv_write(rows, positions, slot_dev, table, q, ka, va, H, G, d, dv, dims, freq, magnitude, error_flag=flag)
+    apart = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+    o.sigmoid_attention_tc(q, ka, va, None, 0, 0, singles, positions, slot_dev, table, apart, H, G, d, dv, None, chunk, scale, bias,
+                           rows[:, gate_offset:], width, error_flag=flag)
+    # together
+    kb, vb = k_pages.to(dtype).to(DEV), v_pages.to(dtype).to(DEV)
+    together = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+    o.sigmoid_attention_tc(None, kb, vb, None, 0, 0, singles, positions, slot_dev, table, together, H, G, d, dv, None, chunk, scale, bias,
+                           rows[:, gate_offset:], width, error_flag=flag, fused_rows=rows, freq=freq, rotary_dim=dims, magnitude=magnitude)
+    torch.cuda.synchronize()
+    assert int(flag.item()) == 0
+    close(together, apart.double().cpu(), dtype, "outputs")
+    close(kb, ka.double().cpu(), dtype, "key pages")
+    close(vb, va.double().cpu(), dtype, "value pages")
+    assert float(together[:6].abs().max()) > 0 and float(together[6].abs().max()) == 0.0
+    changed = (kb.float() != k_pages.to(dtype).to(DEV).float()).flatten(1).any(dim=1).nonzero().flatten().tolist()
+    assert sorted(changed) == sorted(int(table[s, contexts[s] // page]) for s in range(slots))      # one page a request, no other
