@@ -59,6 +59,12 @@ struct Params {
     // product before left them) replaces q; each CTA encodes its token's queries and key (rotary over adjacent pairs of
     // the first rotary_dim elements, frequencies `freq`, sine and cosine times `magnitude`), puts them into its tiles
     // and, with `write_kv`, the key and value into their page.
+    // With `splits` > 1 (steps without portions) the tiles of every token's keys are cut into that many ranges (grid z), each
+    // a CTA of its own that leaves its sum in `partial` ([splits][tokens * nq][dv] 32-bit); sigmoid_attention_sum_kernel
+    // adds a row's ranges in ascending order and applies the gate.  There is nothing to renormalise: the ranges just add.
+    int splits;
+    float* partial;
+    long long rows_total;            // tokens * nq
     const float* fused_rows;
     const float* freq;
     int fused_stride, rotary_dim, write_kv;
@@ -149,9 +155,16 @@ sigmoid_attention_tc_kernel(Params p) {
     const int tok_count = active ? min(p.tokens_per_tile, seg_count - tok0) : 0;
     const int pos_first = seg_start + tok0, pos_last = pos_first + tok_count - 1;
     const int key_end = pos_last + 1;
-    const int key_begin = first_visible(pos_first, p.window, p.chunk);
+    const int key_begin_all = first_visible(pos_first, p.window, p.chunk);
     const int first_of_last = first_visible(max(pos_last, 0), p.window, p.chunk);    // what the CTA's last token sees first
-    const int n_tiles = active ? (key_end - key_begin + KT - 1) / KT : 0;
+    int key_begin_of_cta = key_begin_all, n_tiles = active ? (key_end - key_begin_all + KT - 1) / KT : 0;
+    if (p.splits > 1) {                             // this CTA's range of the tiles
+        const int per = (n_tiles + p.splits - 1) / p.splits;
+        const int first = min(n_tiles, (int)blockIdx.z * per);
+        n_tiles = min(n_tiles, first + per) - first;
+        key_begin_of_cta += first * KT;
+    }
+    const int key_begin = key_begin_of_cta;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), LOADERS);
@@ -185,22 +198,25 @@ sigmoid_attention_tc_kernel(Params p) {
         // ---- loaders: Q once, then the K and V tiles, each thread whole 16-byte pieces ----
         const int lt = threadIdx.x - (WEIGHT_WARPS + 1) * 32;            // 0..127
         const int* table = p.block_table + (size_t)p.slots[q_offset] * p.table_stride;
-        for (int id = lt; id < ROWS * PIECES; id += LOADERS) {
-            const int r = id / PIECES, piece = id % PIECES;
-            const int tok = r / group, head = r % group;
-            const bool valid = tok < tok_count && piece * 8 < p.d;
-            if (p.fused_rows) {
-                // the token's queries from the product's 32-bit row, encoded here (rows beyond its heads are zeros)
-                uint4 piece_bits = make_uint4(0u, 0u, 0u, 0u);
-                if (valid)
-                    piece_bits = encoded_piece(p.fused_rows + (size_t)q_offset * p.fused_stride + (size_t)(kvh * group + head) * p.d, piece * 8,
-                                               seg_start, p.freq, p.rotary_dim, p.magnitude);
-                store_shared_16(q_s + tile_offset<ROWS>(r, piece), piece_bits);
-                continue;
+        auto bring_q = [&](bool encode) {
+            for (int id = lt; id < ROWS * PIECES; id += LOADERS) {
+                const int r = id / PIECES, piece = id % PIECES;
+                const int tok = r / group, head = r % group;
+                const bool valid = tok < tok_count && piece * 8 < p.d;
+                if (encode) {
+                    // the token's queries from the product's 32-bit row, encoded here (rows beyond its heads are zeros)
+                    uint4 piece_bits = make_uint4(0u, 0u, 0u, 0u);
+                    if (valid)
+                        piece_bits = encoded_piece(p.fused_rows + (size_t)q_offset * p.fused_stride + (size_t)(kvh * group + head) * p.d, piece * 8,
+                                                   seg_start, p.freq, p.rotary_dim, p.magnitude);
+                    store_shared_16(q_s + tile_offset<ROWS>(r, piece), piece_bits);
+                    continue;
+                }
+                const size_t src = ((size_t)(q_offset + tok0 + (tok < tok_count ? tok : 0)) * p.nq + kvh * group + head) * p.d + (valid ? piece * 8 : 0);
+                cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
             }
-            const size_t src = ((size_t)(q_offset + tok0 + (tok < tok_count ? tok : 0)) * p.nq + kvh * group + head) * p.d + (valid ? piece * 8 : 0);
-            cp_async_16(q_s + tile_offset<ROWS>(r, piece), p.q + src, valid);
-        }
+        };
+        if (!p.fused_rows) bring_q(false);         // (a fused step encodes its queries below, behind the first tile's copies)
         cp_async_commit();                        // (Q is awaited below, with the first tile's copies already on their way)
         bool ok = true;
         int own_row = -1, own_piece = 0;              // fused step: the page row of the token's own key, if this thread holds a piece of it
@@ -251,6 +267,7 @@ sigmoid_attention_tc_kernel(Params p) {
                 own_piece = piece;
             }
             if (j == 0) {
+                if (p.fused_rows) bring_q(true);
                 asm volatile("cp.async.wait_group 2;" ::: "memory");    // Q has landed (groups complete in the order they were made)
                 fence_async_smem();
                 mbar_arrive(smem_u32(&q_full));
@@ -371,7 +388,21 @@ sigmoid_attention_tc_kernel(Params p) {
         // ---- the row's output times its gate: each of the row's two threads writes half the columns ----
         if (ok && !mbar_wait(smem_u32(&o_done), 0u)) ok = false;
         tc_fence_after();
-        if (ok) {
+        if (ok && p.splits > 1) {
+            // this range's share of the row, as it stands
+            const int t = q_offset + tok0 + (row_ok ? tok : 0);
+            float* dst = p.partial + ((size_t)blockIdx.z * p.rows_total + (size_t)t * p.nq + kvh * group + head) * p.dv;
+#pragma unroll 1
+            for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
+                float o[16];
+                tmem_load16(tmem_o + lane_base + (uint32_t)c0, o);
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4)
+                        if (c0 + c < p.dv) *reinterpret_cast<float4*>(dst + c0 + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                }
+            }
+        } else if (ok) {
             const int t = q_offset + tok0 + (row_ok ? tok : 0);
             float g = 1.0f;
             if (p.gate && row_ok) g = 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.gate_stride + kvh * group + head]));
@@ -395,11 +426,44 @@ sigmoid_attention_tc_kernel(Params p) {
             atomicExch(p.error_flag, 3);
         }
     }
+    if (n_tiles == 0 && p.splits > 1 && active && threadIdx.x < ROWS) {
+        // a range without tiles (fewer tiles than ranges): its share is nothing
+        const int r = threadIdx.x, tok = r / group, head = r % group;
+        if (tok < tok_count) {
+            float* dst = p.partial + ((size_t)blockIdx.z * p.rows_total + (size_t)(q_offset + tok0 + tok) * p.nq + kvh * group + head) * p.dv;
+            for (int c = 0; c < p.dv; ++c) dst[c] = 0.f;
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == WEIGHT_WARPS) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// out[t, h, :] = sigmoid(gate[t, h]) * sum over the ranges, in ascending order, of their shares: a CTA per single token,
+// a thread per (head, 4 elements).
+__global__ void sigmoid_attention_sum_kernel(Params p) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = p.single_rows[blockIdx.x];
+    if (t < 0 || p.slots[t] < 0) return;
+    const int quads = p.dv / 4;
+    for (int item = threadIdx.x; item < p.nq * quads; item += blockDim.x) {
+        const int h = item / quads, c = (item % quads) * 4;
+        const size_t at = ((size_t)t * p.nq + h) * p.dv + c;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int z = 0; z < p.splits; ++z) {
+            const float4 part = *reinterpret_cast<const float4*>(p.partial + (size_t)z * p.rows_total * p.dv + at);
+            sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+        }
+        const float g = p.gate ? 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.gate_stride + h])) : 1.0f;
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(sum.x * g, sum.y * g), hi = __floats2bfloat162_rn(sum.z * g, sum.w * g);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.out + at) = packed;
     }
 }
 
@@ -412,7 +476,9 @@ int launch(const Params& p, cudaStream_t stream) {
             return LIA_ERR_LAUNCH;
         configured = true;
     }
-    return lia_launch(sigmoid_attention_tc_kernel<D>, dim3(p.portion_tiles + p.n_single, p.nkv), dim3(THREADS), smem, stream, p);
+    const int rc = lia_launch(sigmoid_attention_tc_kernel<D>, dim3(p.portion_tiles + p.n_single, p.nkv, p.splits), dim3(THREADS), smem, stream, p);
+    if (rc != LIA_OK || p.splits <= 1) return rc;
+    return lia_launch(sigmoid_attention_sum_kernel, dim3(p.n_single), dim3(256), 0, stream, p);
 }
 }  // namespace
 
@@ -427,19 +493,22 @@ LIA_EXPORT int lia_sigmoid_attention_tc_tokens_per_tile(int group, int d, int dv
 // ([n_segments][3] int32: first batch index, first position, count) lists the portions of several tokens and
 // `portion_tiles` = sum over them of ceil(count / tokens_per_tile); `single_rows` lists the n_single batch indices of
 // single tokens, whose positions come from `positions`.  head_bias, gate, gate_stride, window, chunk: as there.
-// `fused_rows` (optional, only for a step without portions): see Params; q is then not read.
+// `fused_rows` (optional, only for a step without portions): see Params; q is then not read.  `splits` > 1 (only without
+// portions): see Params; `partial` then holds splits * n_tokens * nq * dv 32-bit words, n_tokens the tokens that out covers.
 LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                         int n_segments, int portion_tiles, const int* single_rows, int n_single,
                                         const int* positions, const int* slots, const int* block_table, int table_stride,
                                         void* out, int nq, int nkv, int d, int dv, int page_size, int window, int chunk,
                                         float scale, const float* head_bias, const float* gate, int gate_stride,
                                         int num_pages, const float* fused_rows, int fused_stride, const float* freq,
-                                        int rotary_dim, float magnitude, int write_kv, int* error_flag, cudaStream_t stream) {
+                                        int rotary_dim, float magnitude, int write_kv, int splits, float* partial, int n_tokens,
+                                        int* error_flag, cudaStream_t stream) {
     if (portion_tiles + n_single <= 0) return LIA_OK;
     if (fused_rows && (portion_tiles > 0 || fused_stride < (nq + nkv) * d + nkv * dv || fused_stride % 4 || ((uintptr_t)fused_rows & 15u) ||
                        rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim > 0 && !freq)))
         return LIA_ERR_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535 || portion_tiles < 0 || n_single < 0) return LIA_ERR_SIZE;
+    if (splits < 1 || splits > 32 || (splits > 1 && (portion_tiles > 0 || !partial || n_tokens <= 0 || ((uintptr_t)partial & 15u)))) return LIA_ERR_SIZE;
     const int per_tile = lia_sigmoid_attention_tc_tokens_per_tile(nq / nkv, d, dv);
     if (per_tile == 0) return LIA_ERR_SIZE;
     if (((uintptr_t)q & 15u) || ((uintptr_t)out & 15u) || ((uintptr_t)k_pages & 15u) || ((uintptr_t)v_pages & 15u)) return LIA_ERR_ALIGN;
@@ -452,6 +521,7 @@ LIA_EXPORT int lia_sigmoid_attention_tc(const void* q, const void* k_pages, cons
     p.tokens_per_tile = per_tile; p.d = d; p.dv = dv; p.scale = scale; p.num_pages = num_pages; p.error_flag = error_flag;
     p.fused_rows = fused_rows; p.fused_stride = fused_stride; p.freq = freq; p.rotary_dim = rotary_dim; p.magnitude = magnitude;
     p.write_kv = write_kv;
+    p.splits = splits; p.partial = partial; p.rows_total = (long long)n_tokens * nq;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

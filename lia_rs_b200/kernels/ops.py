@@ -90,7 +90,8 @@ class _Signatures:
     lia_sigmoid_attention_tc_tokens_per_tile = [c_int, c_int, c_int]
     lia_sigmoid_attention_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p]
+                                c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_void_p]
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -729,14 +730,19 @@ def sigmoid_attention_tc_tiles(segments, per_tile: int) -> int:
 def sigmoid_attention_tc(q, k_pages, v_pages, segments, n_segments, portion_tiles, single_rows, positions, slots,
                          block_table, out, nq, nkv, d, dv, window, chunk, scale, head_bias=None, gate=None, gate_stride=0,
                          error_flag=None, label=None, work_bytes=0, work_flops=0, fused_rows=None, freq=None, rotary_dim=0,
-                         magnitude=1.0, write_kv=True):
+                         magnitude=1.0, write_kv=True, splits=1, partial=None):
     """Sigmoid attention on the tcgen05 tensor cores (bfloat16) for the portions listed in `segments` ([n_segments, 3]
     int32: first batch index, first position, count) and the single tokens whose batch indices `single_rows` lists;
     see csrc/sigmoid_attention_tc.cu.  With `fused_rows` (a step of single tokens only: the 32-bit rows of q, k and v
     heads that the product before left, `q` may be None) the kernel applies the pairwise rotary encoding (`freq`,
     `rotary_dim`, `magnitude`) to the queries and the key itself and, with `write_kv`, appends key and value to the pages:
-    no position-encoding kernel runs."""
-    _cuda(q, k_pages, v_pages, segments, single_rows, positions, slots, block_table, out, head_bias, error_flag, freq)
+    no position-encoding kernel runs.  `splits` > 1 (a step without portions): every token's key tiles are cut into that
+    many ranges that run side by side and a second kernel adds them; `partial` is their 32-bit scratch of
+    splits * out.shape[0] * nq * dv words."""
+    _cuda(q, k_pages, v_pages, segments, single_rows, positions, slots, block_table, out, head_bias, error_flag, freq, partial)
+    splits = int(splits)
+    if splits > 1 and (partial is None or partial.dtype != torch.float32 or partial.numel() < splits * out.shape[0] * nq * dv):
+        raise KernelError("sigmoid_attention_tc: the ranges need 32-bit scratch of splits * tokens * heads * head size words")
     if not (k_pages.dtype == v_pages.dtype == out.dtype == torch.bfloat16) or (q is not None and q.dtype != torch.bfloat16):
         raise KernelError("sigmoid_attention_tc is a bfloat16 kernel")
     if tuple(k_pages.shape[2:]) != (nkv, d) or tuple(v_pages.shape[2:]) != (nkv, dv) or out.shape[1] != nq * dv or \
@@ -759,5 +765,6 @@ def sigmoid_attention_tc(q, k_pages, v_pages, segments, n_segments, portion_tile
                                               k_pages.shape[1], int(window or 0), int(chunk or 0), scale, _p(head_bias),
                                               _p(gate), int(gate_stride), k_pages.shape[0], _p(fused_rows),
                                               0 if fused_rows is None else fused_rows.stride(0), _p(freq), int(rotary_dim),
-                                              float(magnitude), 1 if write_kv else 0, _p(error_flag), _stream()),
+                                              float(magnitude), 1 if write_kv else 0, splits, _p(partial) if splits > 1 else None,
+                                              out.shape[0], _p(error_flag), _stream()),
                "sigmoid_attention_tc")

@@ -60,6 +60,17 @@ class PagedSigmoidAttention:
             return ()
         return (self.per_tile, ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile))
 
+    def single_splits(self, ctx, rows: int) -> dict:
+        """Into how many ranges the tensor-core kernel cuts the key tiles of each single token (and their scratch): as
+        many as give every SM a CTA, no more than a token can have tiles at the step's context bucket, its window and
+        its block, at most 8.  It depends on the number of rows and the context bucket alone, as a captured step needs."""
+        longest = min(ctx.context_bucket, self.window or ctx.context_bucket, self.chunk or ctx.context_bucket)
+        splits = max(1, min(ctx.runtime.sm_count // max(1, rows * self.nkv), 8, (longest + 127) // 128))
+        if splits == 1:
+            return {}
+        words = splits * ctx.n_tokens * self.nq * self.dv
+        return dict(splits=splits, partial=ctx.runtime.scratch("sattn.partial", words, torch.float32))
+
     def visible(self, position: int) -> int:
         first = 0
         if self.window:
@@ -89,7 +100,7 @@ class PagedSigmoidAttention:
                                  kv.block_table, out, self.nq, self.nkv, self.d, self.dv, self.window, self.chunk, self.scale,
                                  self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="fused",
                                  work_bytes=work_bytes, fused_rows=projected, freq=freq, rotary_dim=rotary_dim,
-                                 magnitude=magnitude, write_kv=kv.writes)
+                                 magnitude=magnitude, write_kv=kv.writes, **self.single_splits(ctx, ctx.n_tokens))
         return True
 
     def forward(self, ctx, q, kv, out, gate=None, gate_stride=0, rows=None, n_rows=None):
@@ -102,14 +113,16 @@ class PagedSigmoidAttention:
             # a few wanted rows (the last tokens of portions, in a model's last layer): each as a single token
             ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, None, 0, 0, rows[:n_rows], ctx.positions, ctx.slots,
                                      kv.block_table, out, self.nq, self.nkv, self.d, self.dv, self.window, self.chunk,
-                                     self.scale, self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="rows")
+                                     self.scale, self.head_bias, gate, gate_stride, error_flag=ctx.error_flag, label="rows",
+                                     **self.single_splits(ctx, n_rows))
             return
         if self.variant == "tensor":
             tiles = ops.sigmoid_attention_tc_tiles(ctx.segments, self.per_tile) if ctx.n_prefill_segments else 0
             ops.sigmoid_attention_tc(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles,
                                      ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table, out, self.nq, self.nkv,
                                      self.d, self.dv, self.window, self.chunk, self.scale, self.head_bias, gate, gate_stride,
-                                     error_flag=ctx.error_flag, work_bytes=work_bytes, work_flops=work_flops)
+                                     error_flag=ctx.error_flag, work_bytes=work_bytes, work_flops=work_flops,
+                                     **(self.single_splits(ctx, ctx.n_single) if not ctx.n_prefill_segments else {}))
             return
         ops.sigmoid_attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, self.nq,
                                       self.nkv, self.d, self.dv, self.window, self.chunk, self.scale, self.head_bias,

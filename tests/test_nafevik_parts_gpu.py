@@ -325,6 +325,13 @@ def test_sigmoid_attention_on_the_tensor_cores(H, G, d, dv, chunk, window, page)
     assert float(mixed[7].abs().max()) == 0.0 and float(mixed[6].abs().max()) == 0.0       # nobody's row and an absent row
     one_by_one = run([], list(range(0, T, 7)))
     close(one_by_one[::7].view(-1, H, dv), want[::7], dtype, "single tokens")
+    # the same single tokens with their key tiles cut into ranges that a second kernel adds (more ranges than some have tiles)
+    for splits in (2, 3, 5):
+        cut = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
+        o.sigmoid_attention_tc(q, k_pages, v_pages, None, 0, 0, i32(list(range(0, T, 7)) + [6]), positions, nobody.roll(-1), table, cut, H, G, d, dv,
+                               window, chunk, scale, bias.to(DEV), gate_dev, H, error_flag=flag, splits=splits,
+                               partial=torch.full((splits * T * H * dv,), float("nan"), device=DEV))
+        close(cut[::7].view(-1, H, dv), want[::7], dtype, f"single tokens in {splits} ranges")
     # one key decides
     low = torch.full((H,), -14.0)
     for p in (1, 129, 255, 299):
@@ -400,6 +407,14 @@ def test_single_tokens_encoded_and_appended_inside_the_attention_kernel(H, G, d,
     together = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
     o.sigmoid_attention_tc(None, kb, vb, None, 0, 0, singles, positions, slot_dev, table, together, H, G, d, dv, None, chunk, scale, bias,
                            rows[:, gate_offset:], width, error_flag=flag, fused_rows=rows, freq=freq, rotary_dim=dims, magnitude=magnitude)
+    # and with every token's tiles cut into ranges: the range that holds the token's own key appends it
+    kc, vc = k_pages.to(dtype).to(DEV), v_pages.to(dtype).to(DEV)
+    ranged = torch.zeros(n, H * dv, dtype=dtype, device=DEV)
+    o.sigmoid_attention_tc(None, kc, vc, None, 0, 0, singles, positions, slot_dev, table, ranged, H, G, d, dv, None, chunk, scale, bias,
+                           rows[:, gate_offset:], width, error_flag=flag, fused_rows=rows, freq=freq, rotary_dim=dims, magnitude=magnitude,
+                           splits=3, partial=torch.full((3 * n * H * dv,), float("nan"), device=DEV))
+    close(ranged, apart.double().cpu(), dtype, "outputs in ranges")
+    assert torch.equal(kc, kb) and torch.equal(vc, vb)
     torch.cuda.synchronize()
     assert int(flag.item()) == 0
     close(together, apart.double().cpu(), dtype, "outputs")
