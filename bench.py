@@ -416,7 +416,7 @@ def nafevik_pair(size: dict):
     from lia_rs_b200.config import NafevikConfig
     mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"],
              "scale": size["dim"] ** -0.5, "mask": {"size": NAFEVIK_BLOCK},
-             "rot": {"base": 10000.0, "dims": size["dim"], "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+             "rot": {"base": 10000.0, "dims": size["dim"], "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}}
     layer = {"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}}
     nafevik = NafevikConfig.from_dict({
         "architecture": "Nafevik", "vocab": 8192, "width": size["width"], "max_positions": 4096, "norm": {"eps": 1e-5},

@@ -50,12 +50,12 @@ NAFEVIK = {
     "naf-C": dict(
         config={"architecture": "Nafevik", "vocab": 211, "width": 128, "max_positions": 640, "norm": {"eps": 1e-6},
                 "residual_mult": 1.0, "initializer_range": 0.05,
-                "layers": [_layer(4, 1, 64, 64, 0.125, 40, {"base": 20000.0, "dims": 32}, 192),
-                           _layer(4, 1, 64, 64, 0.125, 40, {"base": 20000.0, "dims": 32}, 192)]},
+                "layers": [_layer(4, 1, 64, 64, 0.125, 40, {"base": 25000.0, "dims": 32}, 192),
+                           _layer(4, 1, 64, 64, 0.125, 40, {"base": 25000.0, "dims": 32}, 192)]},
         seed=3, page_size=16, sharpen=1.5),
     "naf-D": dict(
         config={"architecture": "Nafevik", "vocab": 157, "width": 80, "max_positions": 320, "norm": {"eps": 2e-5},
-                "residual_mult": 0.3, "canon": {"taps": 4}, "initializer_range": 0.07,
+                "residual_mult": 0.35, "canon": {"taps": 4}, "initializer_range": 0.07,
                 "layers": [_layer(2, 2, 40, 24, 0.16, 50, {"base": 1000.0, "dims": 40, "scaling":
                                                            {"factor": 2.0, "original": 32, "fast": 8.0, "slow": 1.0}}, 100),
                            _layer(4, 1, 128, 128, 0.09, 64, {"base": 1e6, "dims": 64}, 64)],

@@ -103,7 +103,7 @@ def test_random_weights_load_by_name(tmp_path):
 
 
 def test_scaled_frequencies_against_the_plain_formula():
-    for base, dims, scaling in [(10000.0, 64, None), (20000.0, 48, {"factor": 4.0, "original": 512, "fast": 32.0, "slow": 1.0}),
+    for base, dims, scaling in [(10000.0, 64, None), (30000.0, 56, {"factor": 6.0, "original": 256, "fast": 24.0, "slow": 1.5}),
                                 (500.0, 8, {"factor": 32.0, "original": 4096, "fast": 4.0, "slow": 2.0}),
                                 (1e6, 128, {"factor": 1.5, "original": 64, "fast": 64.0, "slow": 0.5})]:
         freq, magnitude = scaled_frequencies(base, dims, scaling)
