@@ -117,3 +117,150 @@ LIA_EXPORT int lia_attention_generic(const void* q, const void* k_pages, const v
         return LIA_ERR_DTYPE;
     return lia_check_launch();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same walk for attention whose keys come in up to two parts and whose values have a size of their own:
+//   score(t, h, j) = scale * (q1[t, h] . k1[j, g] + q2[t, h] . k2[j, g]),   out[t, h] = sum_j p_j v[j, g]
+// with k1, k2 and v in pages of their own, indexed by the same page numbers (k2 may be absent).  `v_stride` is the
+// length of a (row, kv head) record of the value pages, of which the first dv elements are the value: a value that is a
+// leading part of the first key part (attention through a shared latent: k1 = v = the latent, k2 = the rotated part)
+// passes the k1 pages as values with v_stride = dk1.  q1, q2 and out are addressed by a token stride and a head stride,
+// so that heads may lie side by side in a token's row or in planes of their own.  `sink`: one is added to the softmax's
+// denominator (a key of score 0 that has no value).  Sizes: dk1 + dk2 up to 1,024, dv up to 512.
+namespace {
+constexpr int GENERAL_MAX_DK = 1024;
+
+template <typename T, int DVC>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_general_kernel(const T* __restrict__ q1, long long q1_ts, long long q1_hs, const T* __restrict__ q2,
+                         long long q2_ts, long long q2_hs, const T* __restrict__ k1_pages, int dk1,
+                         const T* __restrict__ k2_pages, int dk2, const T* __restrict__ v_pages, int v_stride, int dv,
+                         const int* __restrict__ positions, const int* __restrict__ slots,
+                         const int* __restrict__ block_table, int table_stride, const int* __restrict__ rows,
+                         T* __restrict__ out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv,
+                         int page_size, int window, float scale, int sink, int num_pages, int* __restrict__ error_flag) {
+    extern __shared__ float q_general[];                    // [WARPS][dk1 + dk2]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)n_tokens * nq) return;
+    const int t = rows ? rows[item / nq] : (int)(item / nq);
+    const int h = (int)(item % nq);
+    if (t < 0) return;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const int kvh = h / (nq / nkv);
+    float* qs = q_general + (size_t)warp * (dk1 + dk2);
+    const T* q1row = q1 + (size_t)t * q1_ts + (size_t)h * q1_hs;
+    for (int i = lane; i < dk1; i += 32) qs[i] = to_float(q1row[i]);
+    if (dk2 > 0) {
+        const T* q2row = q2 + (size_t)t * q2_ts + (size_t)h * q2_hs;
+        for (int i = lane; i < dk2; i += 32) qs[dk1 + i] = to_float(q2row[i]);
+    }
+    __syncwarp();
+    const int* table = block_table + (size_t)slot * table_stride;
+    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    float acc[DVC];
+#pragma unroll
+    for (int c = 0; c < DVC; ++c) acc[c] = 0.f;
+    // with a sink the walk starts from a key of score 0 that has been seen already: maximum 0, sum exp(0 - 0) = 1
+    float running_max = sink ? 0.f : -INFINITY, running_sum = sink ? 1.f : 0.f;
+
+    for (int base = first; base <= pos; base += 32) {
+        const int j = base + lane;
+        bool valid = j <= pos;
+        int row = 0;
+        float score = -INFINITY;
+        if (valid) {
+            row = cache_row_of(table, j, page_size, -1, num_pages, error_flag);
+            valid = row >= 0;
+            row = valid ? row : 0;
+        }
+        if (valid) {
+            const T* krow = k1_pages + ((size_t)row * nkv + kvh) * dk1;
+            float dot = 0.f;
+            for (int i = 0; i < dk1; ++i) dot = fmaf(qs[i], to_float(krow[i]), dot);
+            if (dk2 > 0) {
+                const T* k2row = k2_pages + ((size_t)row * nkv + kvh) * dk2;
+                for (int i = 0; i < dk2; ++i) dot = fmaf(qs[dk1 + i], to_float(k2row[i]), dot);
+            }
+            score = dot * scale;
+        }
+        const float chunk_max = warp_max(score);
+        const float new_max = fmaxf(running_max, chunk_max);
+        if (new_max == -INFINITY) continue;                  // no key of this chunk has a page: nothing to add
+        const float correction = expf(running_max - new_max);
+        const float p = valid ? expf(score - new_max) : 0.f;
+        running_sum = running_sum * correction + warp_sum(p);
+        running_max = new_max;
+#pragma unroll
+        for (int c = 0; c < DVC; ++c) acc[c] *= correction;
+        const int count = min(32, pos - base + 1);
+        for (int jj = 0; jj < count; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const int rj = __shfl_sync(0xffffffffu, row, jj);
+            const T* vrow = v_pages + ((size_t)rj * nkv + kvh) * v_stride;
+#pragma unroll
+            for (int c = 0; c < DVC; ++c) {
+                const int i = c * 32 + lane;
+                if (i < dv) acc[c] = fmaf(pj, to_float(vrow[i]), acc[c]);
+            }
+        }
+    }
+    T* orow = out + (size_t)t * o_ts + (size_t)h * o_hs;
+    const float inv = running_sum > 0.f ? 1.0f / running_sum : 0.f;
+#pragma unroll
+    for (int c = 0; c < DVC; ++c) {
+        const int i = c * 32 + lane;
+        if (i < dv) orow[i] = from_float<T>(acc[c] * inv);
+    }
+}
+
+template <typename T>
+int launch_general(const void* q1, long long q1_ts, long long q1_hs, const void* q2, long long q2_ts, long long q2_hs,
+                   const void* k1_pages, int dk1, const void* k2_pages, int dk2, const void* v_pages, int v_stride, int dv,
+                   const int* positions, const int* slots, const int* block_table, int table_stride, const int* rows,
+                   void* out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv, int page_size, int window,
+                   float scale, int sink, int num_pages, int* error_flag, cudaStream_t stream) {
+    const long long blocks = ((long long)n_tokens * nq + WARPS - 1) / WARPS;
+    if (blocks > 2147483647LL) return LIA_ERR_SIZE;
+    const size_t smem = (size_t)WARPS * (dk1 + dk2) * sizeof(float);
+    const int chunks = (dv + 31) / 32;
+#define LIA_GENERAL(DVC)                                                                                              \
+    return lia_launch(attention_general_kernel<T, DVC>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, stream,       \
+                      (const T*)q1, q1_ts, q1_hs, (const T*)q2, q2_ts, q2_hs, (const T*)k1_pages, dk1,                \
+                      (const T*)k2_pages, dk2, (const T*)v_pages, v_stride, dv, positions, slots, block_table,        \
+                      table_stride, rows, (T*)out, o_ts, o_hs, n_tokens, nq, nkv, page_size, window, scale, sink,     \
+                      num_pages, error_flag)
+    if (chunks <= 2) LIA_GENERAL(2);
+    if (chunks <= 4) LIA_GENERAL(4);
+    if (chunks <= 8) LIA_GENERAL(8);
+    LIA_GENERAL(16);
+#undef LIA_GENERAL
+}
+}  // namespace
+
+LIA_EXPORT int lia_attention_general(const void* q1, long long q1_ts, long long q1_hs, const void* q2, long long q2_ts,
+                                     long long q2_hs, const void* k1_pages, int dk1, const void* k2_pages, int dk2,
+                                     const void* v_pages, int v_stride, int dv, int dtype, const int* positions,
+                                     const int* slots, const int* block_table, int table_stride, const int* rows,
+                                     void* out, long long o_ts, long long o_hs, int n_tokens, int nq, int nkv,
+                                     int page_size, int window, float scale, int sink, int num_pages, int* error_flag,
+                                     cudaStream_t stream) {
+    if (n_tokens <= 0) return LIA_OK;
+    if (nq <= 0 || nkv <= 0 || nq % nkv || dk1 <= 0 || dk2 < 0 || dk1 + dk2 > GENERAL_MAX_DK || dv <= 0 || dv > 512 ||
+        v_stride < dv || page_size <= 0 || (dk2 > 0 && (!q2 || !k2_pages)))
+        return LIA_ERR_SIZE;
+    if (dtype == LIA_F32)
+        return launch_general<float>(q1, q1_ts, q1_hs, q2, q2_ts, q2_hs, k1_pages, dk1, k2_pages, dk2, v_pages, v_stride,
+                                     dv, positions, slots, block_table, table_stride, rows, out, o_ts, o_hs, n_tokens, nq,
+                                     nkv, page_size, window, scale, sink, num_pages, error_flag, stream);
+    if (dtype == LIA_BF16)
+        return launch_general<__nv_bfloat16>(q1, q1_ts, q1_hs, q2, q2_ts, q2_hs, k1_pages, dk1, k2_pages, dk2, v_pages,
+                                             v_stride, dv, positions, slots, block_table, table_stride, rows, out, o_ts,
+                                             o_hs, n_tokens, nq, nkv, page_size, window, scale, sink, num_pages,
+                                             error_flag, stream);
+    return LIA_ERR_DTYPE;
+}

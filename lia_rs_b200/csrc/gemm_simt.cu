@@ -22,8 +22,12 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, int ldw,
-                 TO* __restrict__ out, int ldo, int M, int N, int K, float alpha) {
+                 TO* __restrict__ out, int ldo, int M, int N, int K, float alpha, long long a_batch,
+                 long long w_batch, long long out_batch) {
     constexpr int NW = (MODE == GEMM_SWIGLU) ? 2 : 1;
+    A += (size_t)blockIdx.z * a_batch;                      // one product per blockIdx.z (a single one: all zero)
+    W += (size_t)blockIdx.z * w_batch;
+    out += (size_t)blockIdx.z * out_batch;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[NW][BK][BN + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -93,12 +97,14 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, in
 
 template <typename TA, typename TW, typename TO>
 int launch_modes(int mode, const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M,
-                 int N, int K, float alpha, cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (grid.y > 65535) return LIA_ERR_SIZE;
+                 int N, int K, float alpha, cudaStream_t stream, int batch = 1, long long a_batch = 0,
+                 long long w_batch = 0, long long out_batch = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || batch < 1 || batch > 65535) return LIA_ERR_SIZE;
 #define LIA_GEMM(MODE)                                                                          \
     gemm_simt_kernel<TA, TW, TO, MODE><<<grid, 256, 0, stream>>>((const TA*)A, lda, (const TW*)W, \
-                                                                 ldw, (TO*)out, ldo, M, N, K, alpha)
+                                                                 ldw, (TO*)out, ldo, M, N, K, alpha, \
+                                                                 a_batch, w_batch, out_batch)
     if (mode == GEMM_STORE) LIA_GEMM(GEMM_STORE);
     else if (mode == GEMM_ACCUM) LIA_GEMM(GEMM_ACCUM);
     else if (mode == GEMM_SWIGLU) LIA_GEMM(GEMM_SWIGLU);
@@ -125,5 +131,27 @@ LIA_EXPORT int lia_gemm_simt(int mode, const void* A, int a_dtype, int lda, cons
     if (a_dtype == LIA_BF16 && w_dtype == LIA_BF16 && out_dtype == LIA_BF16)
         return launch_modes<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(mode, A, lda, W, ldw, out, ldo, M,
                                                                          N, K, alpha, stream);
+    return LIA_ERR_DTYPE;
+}
+
+// `batch` products of one shape in one launch: product b reads A + b a_batch, W + b w_batch and writes out + b out_batch
+// (strides in elements).  The products of the heads of an attention whose keys and values are expanded from a shared
+// latent are of this kind: every head has a matrix of its own and rows of its own.
+LIA_EXPORT int lia_gemm_simt_batched(int mode, const void* A, int a_dtype, int lda, long long a_batch, const void* W,
+                                     int w_dtype, int ldw, long long w_batch, void* out, int out_dtype, int ldo,
+                                     long long out_batch, int batch, int M, int N, int K, float alpha,
+                                     cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return LIA_OK;
+    if (K <= 0 || lda < K || ldw < K || ldo < N || mode == GEMM_SWIGLU) return LIA_ERR_SIZE;
+    if (mode == GEMM_ACCUM && out_dtype != LIA_F32) return LIA_ERR_DTYPE;
+    if (a_dtype == LIA_F32 && w_dtype == LIA_F32 && out_dtype == LIA_F32)
+        return launch_modes<float, float, float>(mode, A, lda, W, ldw, out, ldo, M, N, K, alpha, stream, batch, a_batch,
+                                                 w_batch, out_batch);
+    if (a_dtype == LIA_BF16 && w_dtype == LIA_BF16 && out_dtype == LIA_F32)
+        return launch_modes<__nv_bfloat16, __nv_bfloat16, float>(mode, A, lda, W, ldw, out, ldo, M, N, K, alpha, stream,
+                                                                 batch, a_batch, w_batch, out_batch);
+    if (a_dtype == LIA_BF16 && w_dtype == LIA_BF16 && out_dtype == LIA_BF16)
+        return launch_modes<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(mode, A, lda, W, ldw, out, ldo, M, N, K, alpha,
+                                                                         stream, batch, a_batch, w_batch, out_batch);
     return LIA_ERR_DTYPE;
 }

@@ -44,7 +44,7 @@ class Engine:
         """`model_dir`: a folder with config.json and model.safetensors (or a sharded index).
         `max_tokens`: tokens the page pool of each cache group holds; `max_seqs`: request slots;
         `max_batch_tokens`: most tokens one step may bring; `max_context`: most positions of one
-        request (default: the model's max_position_embeddings);
+        request (default: the model's limit; the pool's size for a design that has none);
         `profile`: time every kernel class with CUDA events (`profile_summary()`); steps then run launch by launch,
         never as graphs (the reference's LIA_PROFILE likewise: src/inference/huggingface/minicpm5.rs:14-17).  It can
         be switched at any time by setting `engine.profile`;
@@ -72,8 +72,9 @@ class Engine:
         self.page_size = int(page_size)
         self.max_seqs = int(max_seqs)
         self.max_batch_tokens = int(max_batch_tokens)
-        self.max_context = int(max_context or self.spec.max_positions)
-        if self.max_context > self.spec.max_positions:
+        # a design without a limit of its own: as far as the page pool could carry one request
+        self.max_context = int(max_context or self.spec.max_positions or max(int(max_tokens), self.page_size))
+        if self.spec.max_positions is not None and self.max_context > self.spec.max_positions:
             raise ValueError(f"max_context {self.max_context} exceeds the model's {self.spec.max_positions} positions")
         num_pages = max(1, (int(max_tokens) + self.page_size - 1) // self.page_size)
         self.cache = CacheManager(self.spec.cache_requests(), self.spec.state_requests(), num_pages,

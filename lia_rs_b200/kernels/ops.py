@@ -93,6 +93,29 @@ class _Signatures:
                                 c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_int,
                                 c_void_p, c_void_p]
 
+    lia_norm_residual = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                         c_void_p]
+    lia_activation_rows = [c_void_p, ctypes.c_longlong, c_void_p, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]
+    lia_attention_general = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong,
+                             c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                             c_int, c_void_p, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int, c_int,
+                             c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+    lia_qkv_prepare = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float,
+                       c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lia_latent_prepare = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_float, c_void_p, c_int,
+                          c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lia_causal_conv = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+    lia_conv_state_update = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_void_p]
+    lia_selective_scan = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_void_p,
+                          c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_void_p]
+    lia_gemm_simt_batched = [c_int, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, ctypes.c_longlong,
+                             c_void_p, c_int, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p]
+
 
 def dtype_code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
@@ -768,3 +791,177 @@ def sigmoid_attention_tc(q, k_pages, v_pages, segments, n_segments, portion_tile
                                               float(magnitude), 1 if write_kv else 0, splits, _p(partial) if splits > 1 else None,
                                               out.shape[0], _p(error_flag), _stream()),
                "sigmoid_attention_tc")
+
+
+# ---- parts of decoders with a norm on both sides of a sublayer, attention through a latent, attention with a sink,
+# ---- and a recurrent mixer with input-dependent decay
+
+ACT_NONE, ACT_GELU_TANH, ACT_SILU = 0, 1, 2
+
+
+def _f32(*tensors):
+    for t in tensors:
+        if t is not None and t.dtype != torch.float32:
+            raise KernelError("this kernel takes its 32-bit operands as float32 tensors")
+
+
+def norm_residual(y, weight, residual, eps: float, bias=None, next_weight=None, next_out=None, next_eps: float = 0.0):
+    """residual += rms(y + bias) * weight; with `next_out` also next_out = rms(residual) * next_weight, in one pass over
+    the rows; see csrc/norm_residual.cu.  y, residual, the weights and the bias are 32-bit."""
+    _cuda(y, weight, residual, bias, next_weight, next_out)
+    _f32(y, weight, residual, bias, next_weight)
+    rows, hidden = residual.shape
+    if tuple(y.shape) != (rows, hidden) or weight.numel() != hidden or (bias is not None and bias.numel() != hidden) or \
+            (next_out is not None and (next_weight is None or next_weight.numel() != hidden or tuple(next_out.shape) != (rows, hidden))):
+        raise KernelError("norm_residual: rows of one width, weights and bias of that width")
+    with _timed("norm_residual", nbytes=(3 + (1 if next_out is not None else 0)) * rows * hidden * 4):
+        _check(lib().lia_norm_residual(_p(y), _p(bias), _p(weight), _p(residual), _p(next_weight), _p(next_out),
+                                       dtype_code(next_out.dtype) if next_out is not None else F32, rows, hidden, eps,
+                                       next_eps, _stream()), "norm_residual")
+
+
+def activation_rows(source, out, act: int = ACT_NONE):
+    """out[r, :] = act(source[r, :]) for 32-bit rows `source` (any row stride); see csrc/norm_residual.cu."""
+    if not (source.is_cuda and out.is_cuda) or source.dtype != torch.float32 or source.dim() != 2 or out.dim() != 2 or \
+            source.shape != out.shape or source.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("activation_rows: 32-bit rows in, rows of the same shape out")
+    with _timed("activation_rows", nbytes=source.numel() * 4 + out.numel() * out.element_size()):
+        _check(lib().lia_activation_rows(_p(source), source.stride(0), _p(out), dtype_code(out.dtype), out.stride(0),
+                                         source.shape[0], source.shape[1], int(act), _stream()), "activation_rows")
+
+
+def attention_general(q1, q1_strides, q2, q2_strides, k1_pages, k2_pages, v_pages, v_stride, dv, positions, slots,
+                      block_table, out, out_strides, n_tokens, nq, nkv, window, scale, sink=False, rows=None,
+                      error_flag=None, label=None, work_bytes=0):
+    """Softmax attention whose keys come in up to two parts (k1 [pages, page, nkv, dk1] with q1, k2 [.., dk2] with q2; k2
+    and q2 may be None) and whose values are the first `dv` of every `v_stride` elements of `v_pages`; q1, q2 and out
+    are addressed by (token stride, head stride) in elements; `sink` adds one to the denominator; see
+    csrc/attention_generic.cu.  For every token of the batch, or for the batch indices `rows`."""
+    _cuda(k1_pages, k2_pages, v_pages, positions, slots, block_table, rows, error_flag)
+    for t in (q1, q2, out):
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels need CUDA tensors")
+    if not (q1.dtype == k1_pages.dtype == v_pages.dtype == out.dtype) or (k2_pages is not None and
+                                                                          (q2 is None or q2.dtype != q1.dtype or k2_pages.dtype != q1.dtype)):
+        raise KernelError("attention: q, cache and out must have one element type")
+    dk1 = k1_pages.shape[-1]
+    dk2 = 0 if k2_pages is None else k2_pages.shape[-1]
+    n = n_tokens if rows is None else rows.shape[0]
+    q2s = q2_strides if q2 is not None else (0, 0)
+    with _timed("attention_general", label, work_bytes):
+        _check(lib().lia_attention_general(_p(q1), q1_strides[0], q1_strides[1], _p(q2), q2s[0], q2s[1], _p(k1_pages), dk1,
+                                           _p(k2_pages), dk2, _p(v_pages), int(v_stride), int(dv), dtype_code(q1.dtype),
+                                           _p(positions), _p(slots), _p(block_table), block_table.shape[1], _p(rows),
+                                           _p(out), out_strides[0], out_strides[1], n, nq, nkv, k1_pages.shape[1],
+                                           int(window or 0), scale, 1 if sink else 0, k1_pages.shape[0], _p(error_flag),
+                                           _stream()), "attention_general")
+
+
+def qkv_prepare(rows, bias, q_norm, k_norm, eps, freq, rot_dims, vmix_mode, vmix_lambda, v_first, positions, slots,
+                block_table, q_out, k_pages, v_pages, nq, nkv, d, dv, write_kv=True, error_flag=None):
+    """Bias, per-head RMS norm of q and k, rotate-half encoding, value mixing and the append to the pages for the
+    32-bit rows [q | k | v] of a product; see csrc/qk_prepare.cu."""
+    _cuda(bias, q_norm, k_norm, freq, v_first, positions, slots, block_table, q_out, k_pages, v_pages, error_flag)
+    _f32(rows, bias, q_norm, k_norm, freq, v_first)
+    if not rows.is_cuda or rows.stride(1) != 1 or rows.shape[1] < (nq + nkv) * d + nkv * dv:
+        raise KernelError("qkv_prepare takes 32-bit rows of q, k and v heads")
+    if not (q_out.dtype == k_pages.dtype == v_pages.dtype) or tuple(k_pages.shape[2:]) != (nkv, d) or \
+            tuple(v_pages.shape[2:]) != (nkv, dv) or tuple(q_out.shape) != (rows.shape[0], nq * d):
+        raise KernelError("qkv_prepare: q and the pages must have one element type and the heads' sizes")
+    with _timed("qkv_prepare"):
+        _check(lib().lia_qkv_prepare(_p(rows), rows.stride(0), _p(bias), _p(q_norm), _p(k_norm), float(eps), _p(freq),
+                                     int(rot_dims), int(vmix_mode), float(vmix_lambda), _p(v_first), _p(positions),
+                                     _p(slots), _p(block_table), block_table.shape[1], _p(q_out), _p(k_pages), _p(v_pages),
+                                     dtype_code(q_out.dtype), rows.shape[0], nq, nkv, d, dv, k_pages.shape[1],
+                                     k_pages.shape[0], 1 if write_kv else 0, _p(error_flag), _stream()), "qkv_prepare")
+
+
+def latent_prepare(q_rows, shared_rows, latent_norm, eps, freq, rot_dims, positions, slots, block_table, q_plain,
+                   q_rotated, latent_pages, key_pages, heads, d, dr, rank, write_kv=True, error_flag=None):
+    """For attention through a latent: norm and append of the latent, encoding and append of the shared key part,
+    the queries' unrotated parts as planes [heads, tokens, d] and their rotated parts encoded [tokens, heads dr]; see
+    csrc/qk_prepare.cu."""
+    _cuda(latent_norm, freq, positions, slots, block_table, q_plain, q_rotated, latent_pages, key_pages, error_flag)
+    _f32(q_rows, shared_rows, latent_norm, freq)
+    n = q_rows.shape[0]
+    if q_rows.stride(1) != 1 or shared_rows.stride(1) != 1 or q_rows.shape[1] < heads * (d + dr) or \
+            shared_rows.shape[1] < rank + dr or shared_rows.shape[0] != n:
+        raise KernelError("latent_prepare takes 32-bit query rows and shared rows of one step")
+    if not (q_plain.dtype == q_rotated.dtype == latent_pages.dtype == key_pages.dtype) or q_plain.numel() != heads * n * d \
+            or q_rotated.numel() != n * heads * dr or latent_pages.shape[-1] != rank or key_pages.shape[-1] != dr:
+        raise KernelError("latent_prepare: outputs and pages must have one element type and the parts' sizes")
+    with _timed("latent_prepare"):
+        _check(lib().lia_latent_prepare(_p(q_rows), q_rows.stride(0), _p(shared_rows), shared_rows.stride(0),
+                                        _p(latent_norm), float(eps), _p(freq), int(rot_dims), _p(positions), _p(slots),
+                                        _p(block_table), block_table.shape[1], _p(q_plain), _p(q_rotated),
+                                        _p(latent_pages), _p(key_pages), dtype_code(q_plain.dtype), n, heads, d, dr, rank,
+                                        latent_pages.shape[1], latent_pages.shape[0], 1 if write_kv else 0,
+                                        _p(error_flag), _stream()), "latent_prepare")
+
+
+CONV_MAX_TAPS = 8
+SCAN_MAX_STATES = 256
+
+
+def causal_conv(x, taps_weight, bias, state, positions, slots, out, out_copy=None, act: int = 0):
+    """out[t, c] = act(bias[c] + sum_j taps[c, j] x[t - n + 1 + j, c]) along each request's run, earlier inputs from
+    `state` [slots, n - 1, channels]; `x` 32-bit rows (any stride, the first `channels` columns); act 1: SiLU.  The
+    state is read, not changed: `conv_state_update` follows.  See csrc/selective_scan.cu."""
+    _cuda(taps_weight, bias, positions, slots, out, out_copy)
+    _f32(x, taps_weight, bias, state, out)
+    n, channels = out.shape
+    taps = taps_weight.shape[1]
+    if x.stride(1) != 1 or x.shape[0] != n or x.shape[1] < channels or taps_weight.shape[0] != channels or \
+            (taps > 1 and (tuple(state.shape[1:]) != (taps - 1, channels) or not state[0].is_contiguous())):
+        raise KernelError("causal_conv: rows of at least `channels` columns, taps [channels, n], state [slots, n - 1, channels]")
+    with _timed("causal_conv", nbytes=2 * n * channels * 4):
+        _check(lib().lia_causal_conv(_p(x), x.stride(0), _p(taps_weight), _p(bias), _p(state),
+                                     state.stride(0) if state is not None else 0, _p(positions), _p(slots),
+                                     _p(out), _p(out_copy), dtype_code(out_copy.dtype) if out_copy is not None else F32, n,
+                                     channels, taps, int(act), _stream()), "causal_conv")
+
+
+def conv_state_update(x, state, positions, slots, channels: int):
+    """state[slot] <- the last taps - 1 inputs of the slot's run in this step (older ones kept from the state)."""
+    _cuda(positions, slots)
+    _f32(x, state)
+    taps = state.shape[1] + 1
+    if not state[0].is_contiguous():
+        raise KernelError("conv_state_update: a slot's state must be contiguous")
+    with _timed("conv_state_update"):
+        _check(lib().lia_conv_state_update(_p(x), x.stride(0), _p(state), state.stride(0), _p(positions), _p(slots),
+                                           x.shape[0], channels, taps, _stream()), "conv_state_update")
+
+
+def selective_scan(x, dt_raw, dt_bias, A, bc, b_offset, c_offset, D, z, state, segments, n_segments, single_rows, slots, out):
+    """The recurrence S <- exp(dt A) S + dt x B, y = (S C + D x) silu(z) with dt = softplus(dt_raw + dt_bias), along the
+    step's runs (`segments` [n, 3] and `single_rows`), state [slots, channels, states] 32-bit; see csrc/selective_scan.cu."""
+    _cuda(x, dt_raw, dt_bias, A, D, segments, single_rows, slots, out)
+    _f32(x, dt_raw, dt_bias, A, bc, D, z, state)
+    n, channels = x.shape
+    states = A.shape[1]
+    n_single = 0 if single_rows is None else single_rows.numel()
+    if tuple(dt_raw.shape) != (n, channels) or tuple(A.shape) != (channels, states) or bc.stride(1) != 1 or z.stride(1) != 1 \
+            or tuple(state.shape[1:]) != (channels, states) or not state[0].is_contiguous() or tuple(out.shape) != (n, channels):
+        raise KernelError("selective_scan: shapes do not agree")
+    with _timed("selective_scan", nbytes=n * channels * (12 + out.element_size())):
+        _check(lib().lia_selective_scan(_p(x), _p(dt_raw), _p(dt_bias), _p(A), _p(bc), bc.stride(0), int(b_offset),
+                                        int(c_offset), _p(D), _p(z), z.stride(0), _p(state), state.stride(0), _p(segments), int(n_segments),
+                                        _p(single_rows), n_single, _p(slots), _p(out), dtype_code(out.dtype), channels,
+                                        states, _stream()), "selective_scan")
+
+
+def gemm_simt_batched(mode, a, w, out, alpha: float = 1.0, label=None):
+    """out[b] (op)= alpha * a[b] @ w[b]^T for 3-D tensors a [B, M, K], w [B, N, K], out [B, M, N] (inner strides 1, any
+    row and batch strides) on the 32-bit pipes; see csrc/gemm_simt.cu."""
+    for t in (a, w, out):
+        if not t.is_cuda or t.dim() != 3 or t.stride(2) != 1:
+            raise KernelError("gemm_simt_batched takes 3-D CUDA tensors with contiguous rows")
+    B, M, K = a.shape
+    N = out.shape[2]
+    if tuple(w.shape) != (B, N, K) or tuple(out.shape) != (B, M, N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    with _timed("gemm_simt", label, work=lambda: _gemm_work(a.reshape(-1, K), w.reshape(-1, K), out.reshape(-1, N))):
+        _check(lib().lia_gemm_simt_batched(mode, _p(a), dtype_code(a.dtype), a.stride(1), a.stride(0), _p(w),
+                                           dtype_code(w.dtype), w.stride(1), w.stride(0), _p(out), dtype_code(out.dtype),
+                                           out.stride(1), out.stride(0), B, M, N, K, alpha, _stream()), "gemm_simt_batched")

@@ -30,7 +30,7 @@ class ScheduleEntry:
 class ModelSpec:
     hidden_size: int
     vocab_size: int
-    max_positions: int
+    max_positions: Optional[int]                    # None: the design has no limit of its own
     layers: list
     final_norm: PartSpec
     schedule: list = field(default_factory=list)

@@ -169,6 +169,9 @@ class Mixer(Part):
     supports_rows = False
     # True: `x` may be a `DeferredNorm` (the part only ever gives it to `linear`, or calls its `tensor()`).
     takes_deferred_norm = False
+    # A 32-bit vector [hidden] that belongs to the mixer's output (the bias of its last product) and that `forward` does
+    # NOT add: the arrangement adds it where it next touches the output (an arrangement that cannot refuses the mixer).
+    output_bias = None
 
     @staticmethod
     def cache_request(params: dict) -> Optional[KVCacheRequest]:

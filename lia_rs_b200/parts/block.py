@@ -1,5 +1,7 @@
 """Arrangements of a layer's parts.
 
+`sandwich` (a norm before and after each sublayer) and `parallel` are described at their classes.
+
 `prenorm`: r = h + s * mixer(norm1(h)); h' = r + s * ffn(norm2(r))
 (src/inference/llama_fusion.rs:41-117; s is MiniCPM's scale_depth / sqrt(layers), 1 for plain
 Llama).  Checkpoint names: input_layernorm, self_attn, post_attention_layernorm, mlp
@@ -66,6 +68,8 @@ class PreNormBlock(Arrangement):
         self.norm1, self.mixer, self.norm2, self.feed_forward = (
             cls(params, tensors, prefix + place, runtime) for (cls, params), place in zip(self._classes(spec), places))
         self.graph_safe = all(part.graph_safe for part in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+        if self.mixer.output_bias is not None:
+            raise ValueError("the pre-norm arrangement does not add a mixer's output bias")
 
     def graph_key(self, ctx) -> tuple:
         return (self.norm1.graph_key(ctx) + self.mixer.graph_key(ctx) + self.norm2.graph_key(ctx) +
@@ -97,6 +101,89 @@ class PreNormBlock(Arrangement):
         if n_rows:
             self.feed_forward.forward(ctx, self._normed(ctx, self.norm2, self.feed_forward, picked), picked, self.scale)
         return picked
+
+
+@register_arrangement("sandwich")
+class SandwichBlock(Arrangement):
+    """A norm before and after each sublayer:
+
+        x <- x + post1(mixer(pre1(x)));   x <- x + post2(feed_forward(pre2(x)))
+
+    The sublayer's output goes to a 32-bit buffer of its own (it cannot join the stream before its norm); one kernel
+    norms it, adds it to the stream and, when many tokens follow, norms the new stream for the next sublayer in the same
+    pass (csrc/norm_residual.cu; with few tokens the next sublayer's first product norms its input itself).  The four
+    norms must be RMS norms (`rms_record`).  The feed-forward may be absent (then there is no pre2 and post2).  A mixer's
+    `output_bias` is added ahead of post1.  `residual_scale` has no meaning here (a norm follows the sublayer) and must
+    be 1.  Checkpoint names: `names["norm1"]`, `["norm1b"]`, `["mixer"]`, `["norm2"]`, `["norm2b"]`, `["feed_forward"]`."""
+
+    PLACES = ("norm1", "norm1b", "norm2", "norm2b")
+
+    @staticmethod
+    def _classes(spec: LayerSpec):
+        """[(class, params, place)] of the norms that exist, the mixer and the feed-forward."""
+        places = SandwichBlock.PLACES if spec.feed_forward is not None else SandwichBlock.PLACES[:2]
+        out = [(lookup(NORMS, spec.norm_at(p).kind, "norm"), spec.norm_at(p).params, p) for p in places]
+        out.append((lookup(MIXERS, spec.mixer.kind, "mixer"), spec.mixer.params, "mixer"))
+        if spec.feed_forward is not None:
+            out.append((lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward"), spec.feed_forward.params, "feed_forward"))
+        return out
+
+    @staticmethod
+    def check(spec: LayerSpec) -> None:
+        for cls, params, _ in SandwichBlock._classes(spec):
+            cls.check_params(params)
+        if float(spec.residual_scale) != 1.0:
+            raise ValueError("the sandwich arrangement takes no residual scale")
+
+    @staticmethod
+    def tensor_specs(spec: LayerSpec, prefix: str) -> list:
+        return [t for cls, params, place in SandwichBlock._classes(spec) for t in cls.tensor_specs(params, prefix + spec.names[place])]
+
+    def __init__(self, spec: LayerSpec, tensors: dict, prefix: str, runtime):
+        self.runtime = runtime
+        parts = {place: cls(params, tensors, prefix + spec.names[place], runtime) for cls, params, place in self._classes(spec)}
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("feed_forward")
+        self.pre1, self.pre2 = parts["norm1"], parts.get("norm2")
+        self.post = {}
+        for place in ("norm1b", "norm2", "norm2b"):
+            if place in parts:
+                record = parts[place].rms_record()
+                if record is None:
+                    raise ValueError("the sandwich arrangement needs RMS norms")
+                self.post[place] = (record[0].to(torch.float32).contiguous(), float(record[1]))
+        self.graph_safe = all(part.graph_safe for part in parts.values())
+        self._parts = list(parts.values())
+
+    def graph_key(self, ctx) -> tuple:
+        key = ()
+        for part in self._parts:
+            key += part.graph_key(ctx)
+        return key
+
+    def forward(self, ctx, residual, kv=None, state=None):
+        ops = self.runtime.ops
+        deferred = DeferredNorm(ctx, self.pre1, residual)
+        x = deferred if self.mixer.takes_deferred_norm else deferred.tensor()
+        y = ctx.buffer("block.sublayer", tuple(residual.shape), torch.float32)
+        y.zero_()
+        self.mixer.forward(ctx, x, y, 1.0, kv=kv, state=state)
+        weight, eps = self.post["norm1b"]
+        if self.feed_forward is None:
+            ops.norm_residual(y, weight, residual, eps, bias=self.mixer.output_bias)
+            return None
+        if self.feed_forward.takes_deferred_norm and residual.shape[0] <= ops.STREAM_MAX_TOKENS:
+            ops.norm_residual(y, weight, residual, eps, bias=self.mixer.output_bias)
+            x = DeferredNorm(ctx, self.pre2, residual, buffer_name="block.x2")
+        else:
+            next_weight, next_eps = self.post["norm2"]
+            x = ctx.buffer("block.x2", tuple(residual.shape), self.runtime.compute_dtype)
+            ops.norm_residual(y, weight, residual, eps, bias=self.mixer.output_bias, next_weight=next_weight, next_out=x,
+                              next_eps=next_eps)
+        y.zero_()
+        self.feed_forward.forward(ctx, x, y, 1.0)
+        weight, eps = self.post["norm2b"]
+        ops.norm_residual(y, weight, residual, eps)
+        return None
 
 
 @register_arrangement("parallel")
@@ -173,6 +260,8 @@ class ParallelBlock(Arrangement):
             self.norm_weight, self.eps = record
             self.conv_weights = [tensors[prefix + name].to(self.norm_weight.dtype).contiguous() for name in names]
         self.graph_safe = all(part.graph_safe for part in parts)
+        if self.mixer.output_bias is not None:
+            raise ValueError("the parallel arrangement does not add a mixer's output bias")
 
     def graph_key(self, ctx) -> tuple:
         key = self.norm.graph_key(ctx) + self.mixer.graph_key(ctx)

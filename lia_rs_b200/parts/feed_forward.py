@@ -10,7 +10,7 @@ import torch
 
 from ..weights import TensorSpec
 from .base import FeedForward, register_feed_forward
-from .linear import ACCUM, SWIGLU, linear, prepare_weight
+from .linear import ACCUM, STORE, SWIGLU, linear, prepare_weight
 
 
 @register_feed_forward("swiglu")
@@ -45,4 +45,54 @@ class SwiGLU(FeedForward):
         rt, n = self.runtime, x.shape[0]
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
         linear(rt, SWIGLU, x, self.w_gate_up, act, error_flag=ctx.error_flag, name="gate_up")
+        linear(rt, ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
+
+
+@register_feed_forward("dense_act")
+class DenseActivation(FeedForward):
+    """Dense feed-forward without a gate: f = Wd act(Wu x), no biases.  `activation`: "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu" or "none".  The up product leaves 32-bit rows; the
+    activation is taken of those and rounded once to the compute element type; the down product adds into the residual
+    stream.  Parameters: hidden, intermediate, activation, and optionally `names`: the checkpoint names of the up and
+    down matrices behind the part's prefix."""
+    graph_safe = True
+    takes_deferred_norm = True
+    NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
+    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2}
+
+    def graph_key(self, ctx) -> tuple:
+        return ()
+
+    @staticmethod
+    def _names(params, prefix):
+        names = {**DenseActivation.NAMES, **params.get("names", {})}
+        return prefix + names["up"], prefix + names["down"]
+
+    @staticmethod
+    def check_params(params):
+        if params.get("activation", "gelu_tanh") not in DenseActivation.ACTIVATIONS:
+            raise ValueError(f"dense feed-forward: activation {params.get('activation')!r} is not one of "
+                             f"{sorted(DenseActivation.ACTIVATIONS)}")
+
+    @staticmethod
+    def tensor_specs(params, prefix):
+        h, i = params["hidden"], params["intermediate"]
+        up, down = DenseActivation._names(params, prefix)
+        return [TensorSpec(up, (i, h)), TensorSpec(down, (h, i))]
+
+    def __init__(self, params, tensors, prefix, runtime):
+        super().__init__(params, tensors, prefix, runtime)
+        self.check_params(params)
+        self.hidden, self.intermediate = int(params["hidden"]), int(params["intermediate"])
+        self.activation = self.ACTIVATIONS[params.get("activation", "gelu_tanh")]
+        up, down = self._names(params, prefix)
+        self.w_up = prepare_weight(tensors[up], runtime)
+        self.w_down = prepare_weight(tensors[down], runtime)
+
+    def forward(self, ctx, x, residual, scale):
+        rt, n = self.runtime, x.shape[0]
+        up = ctx.buffer("ffn.up", (n, self.intermediate), torch.float32)
+        linear(rt, STORE, x, self.w_up, up, error_flag=ctx.error_flag, name="up")
+        act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
+        rt.ops.activation_rows(up, act, self.activation)
         linear(rt, ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")

@@ -1,7 +1,10 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, the weight used as stored
 (src/gpu/kernels/normalization.rs:46-112).  Parameters: hidden, eps, and optionally `tensor`: what follows the
-norm's prefix in the weight's checkpoint name (default "weight")."""
+norm's prefix in the weight's checkpoint name (default "weight"), and `one_plus`: the stored weight w lies around zero and
+the norm multiplies by 1 + w (the sum is taken once, at load, in 32-bit, and kept so)."""
 from __future__ import annotations
+
+import torch
 
 from ..weights import TensorSpec
 from .base import Norm, register_norm
@@ -16,13 +19,16 @@ class RMSNorm(Norm):
 
     @staticmethod
     def tensor_specs(params, prefix):
-        return [TensorSpec(prefix + params.get("tensor", "weight"), (params["hidden"],), kind="norm")]
+        kind = "matrix" if params.get("one_plus") else "norm"          # random weights: around zero, or ones
+        return [TensorSpec(prefix + params.get("tensor", "weight"), (params["hidden"],), kind=kind)]
 
     def __init__(self, params, tensors, prefix, runtime):
         super().__init__(params, tensors, prefix, runtime)
         self.hidden = int(params["hidden"])
         self.eps = float(params["eps"])
         self.weight = tensors[prefix + params.get("tensor", "weight")]     # bfloat16 or, if stored so, float32
+        if params.get("one_plus"):
+            self.weight = (1.0 + self.weight.to(torch.float32)).contiguous()
 
     def forward(self, ctx, x, out, rows_index=None, out_scale=1.0):
         self.runtime.ops.rmsnorm(x, self.weight, out, self.eps, out_scale, rows_index)

@@ -84,6 +84,25 @@ def scaled_frequencies(base: float, rotary_dim: int, scaling=None):
     return freq / factor * blend + freq * (1.0 - blend), 0.1 * math.log(factor) + 1.0
 
 
+def band_scaled_frequencies(base: float, rotary_dim: int, scaling=None):
+    """Frequencies [rotary_dim / 2] in 64-bit of a rotary encoding with f_i = base^(-2i/rotary_dim).
+
+    `scaling` (None: plain) holds `factor`, `low`, `high`, `original`: the interpolation by wavelength bands in which,
+    with l_i = 2 pi / f_i, a pair whose wavelength is shorter than original / high keeps its frequency, one whose
+    wavelength is longer than original / low has it divided by `factor`, and those between are blended,
+        s_i = (original / l_i - low) / (high - low),   f_i' = (1 - s_i) f_i / factor + s_i f_i.
+    Sine and cosine keep their magnitude."""
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    freq = float(base) ** (-2.0 * i / rotary_dim)
+    if not scaling:
+        return freq
+    factor, low, high, original = (float(scaling[key]) for key in ("factor", "low", "high", "original"))
+    wavelength = 2.0 * math.pi / freq
+    blend = (original / wavelength - low) / (high - low)
+    blended = (1.0 - blend) * freq / factor + blend * freq
+    return torch.where(wavelength < original / high, freq, torch.where(wavelength > original / low, freq / factor, blended))
+
+
 @register_position_encoding("rotary_pairs")
 class RotaryPairs(PositionEncoding):
     """Rotary encoding in which element 2i of a head is paired with element 2i+1 (the interleaved layout), over

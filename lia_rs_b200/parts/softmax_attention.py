@@ -1,0 +1,244 @@
+"""Two softmax attentions over the paged cache whose queries, keys and values are more than one product's output.
+
+`sink_attention`: grouped-query attention, q = Wq x + bq, k = Wk x + bk, v = Wv x + bv (biases optional), with
+  * an RMS norm of every q head and every k head over the head's elements, with one weight of the head's size for all
+    q heads and one for all k heads (optional), ahead of the rotation;
+  * rotate-half encoding over the first `rot.dims` elements of a head, frequencies plain or scaled by wavelength bands
+    (`rotary.band_scaled_frequencies`);
+  * values of a head size of their own;
+  * value mixing (optional): the first such layer of a model leaves its values of the step's tokens in a step buffer
+    (`value_mix` "source"), later ones ("mixed") use v <- (1 - lambda) v + lambda v_first, lambda a stored scalar; the
+    mixed values are what the pages hold;
+  * a sink (optional): one is added to the softmax's denominator, p_j = exp(s_j) / (1 + sum exp(s_j)), the weight of
+    a key of score 0 that has no value;
+  * all keys j <= i, or the last `window` of them;
+  * an output projection whose bias (optional) is the mixer's `output_bias`.
+
+`latent_attention`: queries and keys go through latents.  c_q = rms(W_dq x) w; q = W_uq c_q, per head `head_dim`
+unrotated and `rot_dim` rotated elements.  W_dkv x gives `kv_rank` elements whose RMS norm (with a weight) is the latent
+c, and `rot_dim` more that are one rotated key part for all heads.  Head h's key is [W_uk,h c | rotated part], its value
+W_uv,h c.  The pages hold c and the rotated part only (the cache's "keys" are the latents, its "values" the rotated
+parts), so attention runs in the latent's space: the unrotated query is taken through W_uk,h^T once per token,
+q~_h = W_uk,h^T q_h, the score is scale (q~_h . c_j + q_rot,h . r_j), the weighted sum of the latents is taken through
+W_uv,h afterwards, and the heads side by side through W_o.  A window as above; no sink.
+
+Scores, softmax, norms and angles are 32-bit in both.  Which kernel serves which rows: the kernel for every size and
+element type (csrc/attention_generic.cu, `attention_general`); `sink_attention` in bfloat16 with equal key and value
+head sizes that the tensor-core kernels take uses those (`PagedAttention` with its `sink`)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights import TensorSpec
+from .base import DeferredNorm, KVCacheRequest, Mixer, NORMS, lookup, register_mixer
+from .linear import ACCUM, STORE, linear, prepare_weight
+from .rotary import band_scaled_frequencies
+
+
+def _frequencies(rot, device):
+    """(rot_dims, 32-bit frequencies on the device) of a `rot` record {base, dims, scaling} (None: no encoding)."""
+    if not rot or not int(rot["dims"]):
+        return 0, None
+    dims = int(rot["dims"])
+    freq = band_scaled_frequencies(float(rot["base"]), dims, rot.get("scaling"))
+    return dims, freq.to(torch.float32).to(device)
+
+
+def _check_rot(rot, limit, what):
+    if rot is None:
+        return
+    dims = int(rot["dims"])
+    if dims < 0 or dims % 2 or dims > limit or (dims and not float(rot["base"]) > 0):
+        raise ValueError(f"{what}: rot.dims must be even and at most {limit}, rot.base positive")
+    scaling = rot.get("scaling")
+    if scaling and not (float(scaling["high"]) != float(scaling["low"]) and float(scaling["factor"]) > 0
+                        and float(scaling["original"]) > 0 and float(scaling["low"]) > 0 and float(scaling["high"]) > 0):
+        raise ValueError(f"{what}: rot.scaling needs positive factor, original, low and high, low and high apart")
+
+
+@register_mixer("sink_attention")
+class SinkAttention(Mixer):
+    graph_safe = True
+    takes_deferred_norm = True
+    NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "o_bias": "o.b",
+             "q_norm": "q.norm", "k_norm": "k.norm", "mix": "vmix"}
+
+    def graph_key(self, ctx) -> tuple:
+        return ()
+
+    @staticmethod
+    def _names(params, prefix):
+        return {key: prefix + name for key, name in {**SinkAttention.NAMES, **params.get("names", {})}.items()}
+
+    @staticmethod
+    def check_params(params):
+        nq, nkv, d, dv = (int(params[k]) for k in ("heads", "kv_heads", "head_dim", "v_head_dim"))
+        if nq <= 0 or nkv <= 0 or nq % nkv:
+            raise ValueError("attention: heads must be a positive multiple of kv_heads")
+        if not 0 < d <= 1024 or not 0 < dv <= 512:
+            raise ValueError("attention: head_dim must be within 1..1024 and v_head_dim within 1..512 (what the kernel takes)")
+        _check_rot(params.get("rot"), d, "attention")
+        if params.get("value_mix") not in (None, "source", "mixed"):
+            raise ValueError("attention: value_mix is None, 'source' or 'mixed'")
+        if params.get("window") is not None and int(params["window"]) <= 0:
+            raise ValueError("attention: window must be positive or None")
+
+    @staticmethod
+    def tensor_specs(params, prefix):
+        h, nq, nkv, d, dv = (int(params[k]) for k in ("hidden", "heads", "kv_heads", "head_dim", "v_head_dim"))
+        n = SinkAttention._names(params, prefix)
+        specs = [TensorSpec(n["q"], (nq * d, h)), TensorSpec(n["k"], (nkv * d, h)), TensorSpec(n["v"], (nkv * dv, h)),
+                 TensorSpec(n["o"], (h, nq * dv))]
+        if params.get("biases"):
+            specs += [TensorSpec(n["q_bias"], (nq * d,)), TensorSpec(n["k_bias"], (nkv * d,)),
+                      TensorSpec(n["v_bias"], (nkv * dv,)), TensorSpec(n["o_bias"], (h,))]
+        if params.get("qk_norm"):
+            specs += [TensorSpec(n["q_norm"], (d,), kind="norm"), TensorSpec(n["k_norm"], (d,), kind="norm")]
+        if params.get("value_mix"):
+            specs.append(TensorSpec(n["mix"], ()))          # the first such layer stores one too and does not use it
+        return specs
+
+    @staticmethod
+    def cache_request(params):
+        return KVCacheRequest(int(params["kv_heads"]), int(params["head_dim"]), params.get("window"),
+                              v_head_dim=int(params["v_head_dim"]))
+
+    def __init__(self, params, tensors, prefix, runtime):
+        super().__init__(params, tensors, prefix, runtime)
+        self.check_params(params)
+        self.hidden = int(params["hidden"])
+        self.nq, self.nkv = int(params["heads"]), int(params["kv_heads"])
+        self.d, self.dv = int(params["head_dim"]), int(params["v_head_dim"])
+        self.scale, self.window, self.sink = float(params["scale"]), params.get("window"), bool(params.get("sink"))
+        self.eps = float(params.get("norm_eps", 1e-6))
+        n = self._names(params, prefix)
+        device = runtime.device
+        used = (self.nq + self.nkv) * self.d + self.nkv * self.dv
+        self.width = (used + 7) // 8 * 8
+        parts = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]]
+        if self.width > used:
+            parts.append(torch.zeros((self.width - used, self.hidden), dtype=parts[0].dtype, device=parts[0].device))
+        self.w_in = prepare_weight(torch.cat(parts, dim=0), runtime)
+        self.w_o = prepare_weight(tensors[n["o"]], runtime)
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        self.bias_in, self.output_bias = None, None
+        if params.get("biases"):
+            self.bias_in = f32(torch.cat([tensors[n["q_bias"]], tensors[n["k_bias"]], tensors[n["v_bias"]]]))
+            self.output_bias = f32(tensors[n["o_bias"]])
+        self.q_norm = f32(tensors[n["q_norm"]]) if params.get("qk_norm") else None
+        self.k_norm = f32(tensors[n["k_norm"]]) if params.get("qk_norm") else None
+        self.rot_dims, self.freq = _frequencies(params.get("rot"), device)
+        self.mix_mode = {None: 0, "source": 1, "mixed": 2}[params.get("value_mix")]
+        self.mix_lambda = float(tensors[n["mix"]].to(torch.float32)) if self.mix_mode == 2 else 0.0
+
+    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+        rt, n = self.runtime, x.shape[0]
+        nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
+        flag = ctx.error_flag
+        projected = ctx.buffer("sinkattn.in", (n, self.width), torch.float32)
+        linear(rt, STORE, x, self.w_in, projected, error_flag=flag, name="qkv")
+        q = ctx.buffer("sinkattn.q", (n, nq * d), rt.compute_dtype)
+        v_first = ctx.buffer("sinkattn.v_first", (n, nkv * dv), torch.float32) if self.mix_mode else None
+        ops.qkv_prepare(projected, self.bias_in, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
+                        self.mix_mode, self.mix_lambda, v_first, ctx.positions, ctx.slots, kv.block_table, q, kv.k_pages,
+                        kv.v_pages, nq, nkv, d, dv, write_kv=kv.writes, error_flag=flag)
+        o = ctx.buffer("sinkattn.o", (n, nq * dv), rt.compute_dtype)
+        ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, dv, dv, ctx.positions, ctx.slots,
+                              kv.block_table, o, (nq * dv, dv), n, nq, nkv, self.window, self.scale, sink=self.sink,
+                              error_flag=flag)
+        linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+    takes_deferred_norm = True
+    NAMES = {"q_down": "dq", "q_norm": "dq.norm", "q_up": "uq", "kv_down": "dkv", "kv_norm": "dkv.norm", "k_up": "uk",
+             "v_up": "uv", "o": "o"}
+
+    def graph_key(self, ctx) -> tuple:
+        return ()
+
+    @staticmethod
+    def _names(params, prefix):
+        return {key: prefix + name for key, name in {**LatentAttention.NAMES, **params.get("names", {})}.items()}
+
+    @staticmethod
+    def check_params(params):
+        for key in ("heads", "head_dim", "rot_dim", "v_head_dim", "kv_rank", "q_rank"):
+            if int(params[key]) <= 0:
+                raise ValueError(f"latent attention: {key} must be positive")
+        if int(params["kv_rank"]) + int(params["rot_dim"]) > 1024 or int(params["kv_rank"]) > 512:
+            raise ValueError("latent attention: kv_rank at most 512 and kv_rank + rot_dim at most 1024 (what the kernel takes)")
+        _check_rot(params.get("rot"), int(params["rot_dim"]), "latent attention")
+        if params.get("window") is not None and int(params["window"]) <= 0:
+            raise ValueError("latent attention: window must be positive or None")
+
+    @staticmethod
+    def tensor_specs(params, prefix):
+        h, H, d, dr, dv, rank, q_rank = (int(params[k]) for k in ("hidden", "heads", "head_dim", "rot_dim", "v_head_dim",
+                                                                   "kv_rank", "q_rank"))
+        n = LatentAttention._names(params, prefix)
+        return [TensorSpec(n["q_down"], (q_rank, h)), TensorSpec(n["q_norm"], (q_rank,), kind="norm"),
+                TensorSpec(n["q_up"], (H * (d + dr), q_rank)), TensorSpec(n["kv_down"], (rank + dr, h)),
+                TensorSpec(n["kv_norm"], (rank,), kind="norm"), TensorSpec(n["k_up"], (H * d, rank)),
+                TensorSpec(n["v_up"], (H * dv, rank)), TensorSpec(n["o"], (h, H * dv))]
+
+    @staticmethod
+    def cache_request(params):
+        # the pages' "keys" are the latents, their "values" the shared rotated key parts: one record a token for all heads
+        return KVCacheRequest(1, int(params["kv_rank"]), params.get("window"), v_head_dim=int(params["rot_dim"]))
+
+    def __init__(self, params, tensors, prefix, runtime):
+        super().__init__(params, tensors, prefix, runtime)
+        self.check_params(params)
+        self.hidden, self.heads = int(params["hidden"]), int(params["heads"])
+        self.d, self.dr, self.dv = int(params["head_dim"]), int(params["rot_dim"]), int(params["v_head_dim"])
+        self.rank, self.q_rank = int(params["kv_rank"]), int(params["q_rank"])
+        self.scale, self.window = float(params["scale"]), params.get("window")
+        self.eps = float(params.get("norm_eps", 1e-6))
+        n = self._names(params, prefix)
+        H, d, dv, rank = self.heads, self.d, self.dv, self.rank
+        self.w_q_down = prepare_weight(tensors[n["q_down"]], runtime)
+        self.w_q_up = prepare_weight(tensors[n["q_up"]], runtime)
+        self.w_kv_down = prepare_weight(tensors[n["kv_down"]], runtime)
+        # head h's share of the key expansion, transposed: the product that takes a query into the latent's space
+        self.w_k_up_t = prepare_weight(tensors[n["k_up"]].view(H, d, rank).transpose(1, 2), runtime)       # [H, rank, d]
+        self.w_v_up = prepare_weight(tensors[n["v_up"]].view(H, dv, rank), runtime)                         # [H, dv, rank]
+        self.w_o = prepare_weight(tensors[n["o"]], runtime)
+        norm_params = {"hidden": self.q_rank, "eps": self.eps, "tensor": ""}
+        self.q_norm = lookup(NORMS, "rmsnorm", "norm")(norm_params, {n["q_norm"]: tensors[n["q_norm"]]}, n["q_norm"], runtime)
+        self.kv_norm = tensors[n["kv_norm"]].to(torch.float32).contiguous()
+        self.rot_dims, self.freq = _frequencies(params.get("rot"), runtime.device)
+
+    def _head_products(self, mode, a, w, out, name):
+        """out[h] (op)= a[h] @ w[h]^T for every head (3-D tensors, a head a plane)."""
+        ops.gemm_simt_batched(mode, a, w, out, label=name)
+
+    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+        rt, n = self.runtime, x.shape[0]
+        H, d, dr, dv, rank = self.heads, self.d, self.dr, self.dv, self.rank
+        flag, dtype = ctx.error_flag, rt.compute_dtype
+        q_latent = ctx.buffer("latent.cq", (n, self.q_rank), torch.float32)
+        linear(rt, STORE, x, self.w_q_down, q_latent, error_flag=flag, name="q_down")
+        shared = ctx.buffer("latent.shared", (n, rank + dr), torch.float32)
+        linear(rt, STORE, x, self.w_kv_down, shared, error_flag=flag, name="kv_down")
+        q_rows = ctx.buffer("latent.q", (n, H * (d + dr)), torch.float32)
+        linear(rt, STORE, DeferredNorm(ctx, self.q_norm, q_latent, buffer_name="latent.cq_normed"), self.w_q_up, q_rows,
+               error_flag=flag, name="q_up")
+        scratch = ctx.runtime.scratch
+        q_plain = scratch("latent.q_plain", H * n * d, dtype).view(H, n, d)
+        q_rotated = ctx.buffer("latent.q_rot", (n, H * dr), dtype)
+        ops.latent_prepare(q_rows, shared, self.kv_norm, self.eps, self.freq, self.rot_dims, ctx.positions, ctx.slots,
+                           kv.block_table, q_plain, q_rotated, kv.k_pages, kv.v_pages, H, d, dr, rank, write_kv=kv.writes,
+                           error_flag=flag)
+        q_absorbed = scratch("latent.q_absorbed", H * n * rank, dtype).view(H, n, rank)
+        self._head_products(STORE, q_plain, self.w_k_up_t, q_absorbed, "k_up")
+        mixed = scratch("latent.mixed", H * n * rank, dtype).view(H, n, rank)
+        ops.attention_general(q_absorbed, (rank, n * rank), q_rotated, (H * dr, dr), kv.k_pages, kv.v_pages, kv.k_pages,
+                              rank, rank, ctx.positions, ctx.slots, kv.block_table, mixed, (rank, n * rank), n, H, 1,
+                              self.window, self.scale, sink=False, error_flag=flag)
+        o = ctx.buffer("latent.o", (n, H * dv), dtype)
+        self._head_products(STORE, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
+        linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
