@@ -429,20 +429,22 @@ def nafevik_pair(size: dict):
     return {"nafevik": nafevik, "llama": llama}
 
 
-def nafevik_workload(steps, warmup) -> int:
+def pair_workload(name, metric, sizes_table, pair, steps, warmup, context=4096) -> int:
+    """Two or more models of equal sizes side by side: decode at batch 8 and 64 behind 2,048-token prompts, the
+    2,048-token prefill step, and every kernel class's share of those steps with the fraction of its own roofline."""
     import torch
     from lia_rs_b200.engine import Engine
     peak = peaks()
     sampler = ClockSampler()
     sampler.start()
     sizes = {}
-    for name, size in NAFEVIK_SIZES.items():
-        sizes[name] = {}
-        for model, config in nafevik_pair(size).items():
+    for size_name, size in sizes_table.items():
+        sizes[size_name] = {}
+        for model, config in pair(size).items():
             batch = 64
             pool = batch * (PROMPT + MAX_DECODE_STEPS + 64)
             engine = Engine.random(config, seed=3, dtype="bfloat16", page_size=PAGE, max_tokens=pool, max_seqs=batch,
-                                   max_batch_tokens=PROMPT, max_context=4096)
+                                   max_batch_tokens=PROMPT, max_context=context)
             point = {}
             for b in (8, 64):
                 slots = fill(engine, b, PROMPT, 11 + b)
@@ -453,13 +455,59 @@ def nafevik_workload(steps, warmup) -> int:
             ms, drift = time_prefill(engine)
             point["prefill_2048"] = {"ms": round(ms, 4), "tokens_per_s": round(PROMPT / ms * 1e3, 1), "graph_drift": drift}
             point["kernels"] = kernel_shares(engine, 8, peak)
-            sizes[name][model] = point
+            sizes[size_name][model] = point
             del engine
             torch.cuda.empty_cache()
     clocks = sampler.stop()
-    print(json.dumps({"workload": "nafevik", "metric": "Nafevik beside the Llama decoder at equal sizes, four layer runs, bf16",
-                      "data": "synthetic", "dtype": "bf16", "peaks": peak, "clocks": clocks, "sizes": sizes}))
+    print(json.dumps({"workload": name, "metric": metric, "data": "synthetic", "dtype": "bf16", "peaks": peak,
+                      "clocks": clocks, "sizes": sizes}))
     return 0
+
+
+def nafevik_workload(steps, warmup) -> int:
+    return pair_workload("nafevik", "Nafevik beside the Llama decoder at equal sizes, four layer runs, bf16", NAFEVIK_SIZES,
+                         nafevik_pair, steps, warmup)
+
+
+# The Vatunex decoder beside the Llama decoder at equal sizes (--workload vatunex): four layers each.  Vatunex: attention
+# through latents (window of 1,024), attention with a sink (all keys), a selective scan, attention through latents; the
+# Llama decoder: four grouped-query layers of the same width, heads and feed-forward size.  Vocabulary 8,192, random weights.
+VATUNEX_SIZES = {
+    "2B-widths": dict(width=2048, heads=16, kv_heads=2, dim=128, ff=6144, rot_dim=64, kv_rank=512, q_rank=1024,
+                      inner=4096, state=16, dt_rank=128),
+    "0.5B-widths": dict(width=1024, heads=16, kv_heads=2, dim=64, ff=4096, rot_dim=32, kv_rank=256, q_rank=512,
+                        inner=2048, state=16, dt_rank=64),
+}
+VATUNEX_WINDOW = 1024
+
+
+def vatunex_pair(size: dict):
+    from lia_rs_b200 import LlamaConfig
+    from lia_rs_b200.config import VatunexConfig
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    latent = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "dim": size["dim"], "rot_dim": size["rot_dim"], "vdim": size["dim"], "kv_rank": size["kv_rank"],
+        "q_rank": size["q_rank"], "scale": (size["dim"] + size["rot_dim"]) ** -0.5, "mask": {"size": VATUNEX_WINDOW},
+        "rot": {"base": 10000.0, "dims": size["rot_dim"]}}}
+    attention = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["dim"], "scale": size["dim"] ** -0.5,
+        "v_mix": True, "rot": {"base": 10000.0, "dims": size["dim"],
+                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+    scan = {"type": "mamba1", "mlp": mlp, "mixer": {"inner": size["inner"], "state": size["state"], "dt_rank": size["dt_rank"],
+                                                    "conv": 4}}
+    vatunex = VatunexConfig.from_dict({"architecture": "Vatunex", "vocab": 8192, "width": size["width"], "norm": {"eps": 1e-5},
+                                       "layers": [latent, attention, scan, latent]})
+    llama = LlamaConfig.from_dict(dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=size["width"], intermediate_size=size["ff"],
+        num_hidden_layers=4, num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
+        vocab_size=8192, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=4096,
+        initializer_range=0.02, hidden_act="silu", torch_dtype="bfloat16"))
+    return {"vatunex": vatunex, "llama": llama}
+
+
+def vatunex_workload(steps, warmup) -> int:
+    return pair_workload("vatunex", "Vatunex beside the Llama decoder at equal sizes, four layers, bf16", VATUNEX_SIZES,
+                         vatunex_pair, steps, warmup)
 
 
 def main() -> int:
@@ -472,7 +520,7 @@ def main() -> int:
                         help="run fewer layers than the configuration's 40 (both numbers are reported)")
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--no-points", action="store_true", help="skip batch 1 and batch 64")
-    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik"],
+    parser.add_argument("--workload", default=None, choices=["8b-decode", "8b-prefill", "0.5b-mixed", "nafevik", "vatunex"],
                         help="one of the family's other sizes on the workload it is quoted on (prints its own line)")
     parser.add_argument("--device-trace", action="store_true",
                         help="with --workload 0.5b-mixed: one more pass under a trace of the device's kernels; adds "
@@ -493,6 +541,8 @@ def main() -> int:
         args.warmup = 3
     if args.workload == "nafevik":
         return nafevik_workload(args.steps, args.warmup)
+    if args.workload == "vatunex":
+        return vatunex_workload(args.steps, args.warmup)
     if args.workload:
         return other_workload(args.workload, args.steps, args.warmup, trace=args.device_trace)
 

@@ -47,6 +47,7 @@ struct Params {
     int rotary_dim, write_kv, num_pages;
     int cluster;                     // the CTAs of a token's ranges are one cluster (gridDim.z of them) and merge in shared memory
     int all_new;                     // any of a row's keys may have been written by this step's kernels (rows of prompt portions), not only its own
+    int sink;                        // 1: one is added to the softmax's denominator (a key of score 0 without a value), where a token's ranges meet
     int* error_flag;
 };
 
@@ -143,6 +144,7 @@ __device__ __forceinline__ void cluster_merge(const Params& p, uint8_t* smem, in
                 acc[0] += w * v[c].x; acc[1] += w * v[c].y; acc[2] += w * v[c].z; acc[3] += w * v[c].w;
             }
         }
+        if (p.sink) total += exp2f(-top);
         const float inv = total > 0.f ? 1.0f / total : 0.f;
         uint2 packed;
         packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
@@ -511,6 +513,7 @@ attention_decode_kernel(Params p) {
             f[w] = exp2_whole(merge_m[w * 16 + r] - top);             // both are whole numbers (or -infinity)
             total += f[w] * merge_l[w * 16 + r];
         }
+        if (p.sink && !p.cluster && p.n_splits <= 1) total += exp2f(-top);
         const float inv = 1.0f / total;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) merge_f[w * 16 + r] = f[w] * inv;
@@ -598,6 +601,7 @@ attention_decode_kernel(Params p) {
                 acc[0] += w * v[j][0].x; acc[1] += w * v[j][0].y; acc[2] += w * v[j][0].z; acc[3] += w * v[j][0].w;
                 acc[4] += w * v[j][1].x; acc[5] += w * v[j][1].y; acc[6] += w * v[j][1].z; acc[7] += w * v[j][1].w;
             }
+            if (p.sink) total += exp2f(-top);
             const float inv = 1.0f / total;
             uint4 packed;
             packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
@@ -622,6 +626,7 @@ attention_decode_kernel(Params p) {
             total += f;
         }
         total = warp_sum(total);                  // the order of this sum depends on `used` alone
+        if (p.sink) total += exp2f(-top);
         if (lane == 0) totals[r] = total;
     }
     __syncthreads();
@@ -673,6 +678,7 @@ __global__ void attention_merge_kernel(Params p) {
             total += f;
             value += f * p.partial[(at + s) * D + dcol];
         }
+        if (p.sink) total += exp2f(-top);
         p.out[((size_t)t * p.nq + h) * D + dcol] = __float2bfloat16_rn(value / total);
     }
 }
@@ -834,7 +840,8 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
                                     int table_stride, void* out, float* partial, long long partial_floats,
                                     int* counters, int n_tokens, int nq, int nkv, int d, int page_size, int window, float scale,
                                     int split_len, int n_splits, const float* qkv, const float* inv_freq, int rotary_dim,
-                                    int write_kv, int num_pages, int cluster, int all_new, int* error_flag, cudaStream_t stream) {
+                                    int write_kv, int num_pages, int cluster, int all_new, int sink, int* error_flag,
+                                    cudaStream_t stream) {
     if (n_rows <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || split_len < 0 || split_len % TILE_KEYS || n_splits <= 0 ||
         n_splits > 65535)
@@ -855,6 +862,7 @@ LIA_EXPORT int lia_attention_decode(const void* q, const void* k_pages, const vo
     p.error_flag = error_flag;
     p.cluster = cluster ? 1 : 0;
     p.all_new = all_new ? 1 : 0;
+    p.sink = sink ? 1 : 0;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;

@@ -41,6 +41,7 @@ struct PrefillParams {
     float scale_log2;
     int num_pages;
     int* error_flag;                 // raised to 2 when a visible key has no page
+    int sink;                        // 1: one is added to the softmax's denominator (a key of score 0 without a value)
 };
 
 template <int D>
@@ -254,7 +255,7 @@ attention_prefill_kernel(PrefillParams p) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         if (!row_ok[i]) continue;
-        const float inv = 1.0f / row_sum[i];
+        const float inv = 1.0f / (row_sum[i] + (p.sink ? exp2f(-row_max[i]) : 0.f));
 #pragma unroll
         for (int j = 0; j < D / 8; ++j)
             *reinterpret_cast<uint32_t*>(o_row[i] + j * 8 + c) = pack_bf16(o[j][i * 2] * inv, o[j][i * 2 + 1] * inv);
@@ -284,7 +285,7 @@ LIA_EXPORT int lia_attention_prefill_tokens_per_tile(int group) {
 LIA_EXPORT int lia_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                      int n_segments, int n_tiles, const int* slots, const int* block_table,
                                      int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
-                                     float scale, int num_pages, int* error_flag, cudaStream_t stream) {
+                                     float scale, int num_pages, int sink, int* error_flag, cudaStream_t stream) {
     if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
     const int per_tile = lia_attention_prefill_tokens_per_tile(nq / nkv);
@@ -293,7 +294,7 @@ LIA_EXPORT int lia_attention_prefill(const void* q, const void* k_pages, const v
     p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
     p.segments = segments; p.slots = slots; p.block_table = block_table; p.out = (__nv_bfloat16*)out;
     p.n_segments = n_segments; p.table_stride = table_stride; p.nq = nq; p.nkv = nkv; p.page_size = page_size;
-    p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E;
+    p.window = window; p.tokens_per_tile = per_tile; p.scale_log2 = scale * LOG2E; p.sink = sink ? 1 : 0;
     p.num_pages = num_pages; p.error_flag = error_flag;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)

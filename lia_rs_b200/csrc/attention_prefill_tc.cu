@@ -67,6 +67,7 @@ struct Params {
     float* partial_o;                // [splits][tokens * nq][D]
     float* partial_ms;               // [splits][tokens * nq][2]: reference point (a whole number, or -infinity), sum
     long long n_rows_total;          // tokens * nq
+    int sink;                        // 1: one is added to the softmax's denominator (a key of score 0 without a value)
 };
 
 template <int D>
@@ -372,7 +373,7 @@ attention_prefill_tc_kernel(Params p) {
                 }
             }
         } else if (ok) {
-            const float inv = 1.0f / (pair_sum[r] + pair_sum[ROWS + r]);
+            const float inv = 1.0f / (pair_sum[r] + pair_sum[ROWS + r] + (p.sink ? exp2f(-row_max) : 0.f));
             __nv_bfloat16* dst = p.out + ((size_t)(q_offset + tok0 + (row_ok ? tok : 0)) * p.nq + kvh * group + head) * D;
 #pragma unroll 1
             for (int c0 = half * (D / 2); c0 < (half + 1) * (D / 2); c0 += 16) {
@@ -464,6 +465,7 @@ __global__ void __launch_bounds__(128) attention_prefill_merge_kernel(Params p) 
             acc[e + 1] = fmaf(w, v.y, acc[e + 1]);
         }
     }
+    if (p.sink) total += exp2f(-top);                  // the sink joins once, where the ranges meet
     const float inv = 1.0f / total;
     __nv_bfloat16* dst = p.out + row * D + lane * E;
 #pragma unroll
@@ -500,7 +502,7 @@ LIA_EXPORT int lia_attention_prefill_tc_tokens_per_tile(int group, int d) {
 LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, const int* segments,
                                         int n_segments, int n_tiles, const int* slots, const int* block_table,
                                         int table_stride, void* out, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int num_pages, int splits, float* partial, int n_tokens,
+                                        float scale, int num_pages, int splits, float* partial, int n_tokens, int sink,
                                         int* error_flag, cudaStream_t stream) {
     if (n_segments <= 0 || n_tiles <= 0) return LIA_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || nkv > 65535) return LIA_ERR_SIZE;
@@ -520,6 +522,7 @@ LIA_EXPORT int lia_attention_prefill_tc(const void* q, const void* k_pages, cons
     for (int b = 0; b < 31; ++b)
         if (page_size == (1 << b)) p.page_shift = b;
     p.splits = splits;
+    p.sink = sink ? 1 : 0;
     p.n_rows_total = (long long)n_tokens * nq;
     p.partial_o = partial;
     p.partial_ms = partial ? partial + (size_t)splits * p.n_rows_total * d : nullptr;

@@ -51,7 +51,7 @@ class _Signatures:
     lia_wait_probe = [c_int, c_void_p, c_void_p, c_void_p]
     lia_attention_decode = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                            c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_attention_decode_cluster_splits = [c_int, c_int, c_int, c_int]
     lia_attention_decode_ctas_per_sm = [c_int, c_int]
     lia_gemm_tc = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -65,9 +65,9 @@ class _Signatures:
                        c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_stream_stages = [c_int, c_int, c_int, c_int, c_int, c_int]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
     lia_attention_prefill_tc = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_int,
                                 c_void_p, c_void_p]
     lia_attention_prefill_tc_tokens_per_tile = [c_int, c_int]
     lia_select_tokens = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -116,6 +116,9 @@ class _Signatures:
     lia_gemm_simt_batched = [c_int, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, ctypes.c_longlong,
                              c_void_p, c_int, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p]
 
+    lia_latent_attention_accepts = [c_int, c_int]
+    lia_latent_attention = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
 
 def dtype_code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
@@ -474,7 +477,7 @@ DECODE_HEAD_DIMS = (32, 64, 128)       # head sizes the tensor-core attention ke
 
 def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, nq, nkv, d, window,
                      scale, split_len, n_splits, counters=None, qkv=None, inv_freq=None, rotary_dim=0, write_kv=True,
-                     error_flag=None, label=None, work_bytes=0, cluster=False, all_new=False):
+                     error_flag=None, label=None, work_bytes=0, cluster=False, all_new=False, sink=False):
     """Split-key decode attention (bfloat16) for the single-token rows of the batch; see
     csrc/attention_decode.cu.  `partial` is 32-bit scratch for the ranges' partial results.
     `split_len` 0: every row cuts its own visible span into `n_splits` ranges.  `counters` (int32, at
@@ -487,7 +490,8 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
     `attention_decode_cluster_splits`; the ranges of a token then meet in distributed shared memory and neither
     `partial` nor `counters` is used.  `all_new`: the rows may be tokens of this step's prompt portions, so any of
     their keys may have been written by the kernels ahead (otherwise only a row's own key is taken to be of this step,
-    and the kernel fetches older tiles before it waits for those kernels)."""
+    and the kernel fetches older tiles before it waits for those kernels).  `sink`: one is added to the softmax's denominator
+    (a key of score 0 without a value), once, where a token's ranges meet."""
     _cuda(q, k_pages, v_pages, rows, positions, slots, block_table, out, partial, counters, qkv, inv_freq, error_flag)
     if qkv is not None:
         if qkv.dtype != torch.float32 or qkv.shape[1] != (nq + 2 * nkv) * d:
@@ -504,7 +508,7 @@ def attention_decode(q, k_pages, v_pages, rows, positions, slots, block_table, o
                                           0 if partial is None else partial.numel(), _p(counters), q.shape[0], nq, nkv, d,
                                           k_pages.shape[1], int(window or 0), scale, split_len, n_splits, _p(qkv), _p(inv_freq),
                                           int(rotary_dim), 1 if write_kv else 0, k_pages.shape[0], 1 if cluster else 0, 1 if all_new else 0,
-                                          _p(error_flag),
+                                          1 if sink else 0, _p(error_flag),
                                           _stream()),
                "attention_decode")
 
@@ -526,7 +530,7 @@ def attention_prefill_tokens_per_tile(group: int) -> int:
 
 
 def attention_prefill(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                      window, scale, error_flag=None, label=None, work_flops=0):
+                      window, scale, error_flag=None, label=None, work_flops=0, sink=False):
     """Tensor-core attention (bfloat16) for the prompt portions listed in `segments`
     ([n_segments, 3] int32: first batch index, first position, count); see csrc/attention_prefill.cu."""
     _cuda(q, k_pages, v_pages, segments, slots, block_table, out, error_flag)
@@ -535,8 +539,8 @@ def attention_prefill(q, k_pages, v_pages, segments, n_segments, n_tiles, slots,
     with _timed("attention_prefill", label, 0, work_flops):
         _check(lib().lia_attention_prefill(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
                                            _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
-                                           k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], _p(error_flag),
-                                           _stream()), "attention_prefill")
+                                           k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], 1 if sink else 0,
+                                           _p(error_flag), _stream()), "attention_prefill")
 
 
 def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
@@ -546,7 +550,7 @@ def attention_prefill_tc_tokens_per_tile(group: int, d: int) -> int:
 
 
 def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slots, block_table, out, nq, nkv, d,
-                         window, scale, error_flag=None, label=None, work_flops=0, splits=1, partial=None):
+                         window, scale, error_flag=None, label=None, work_flops=0, splits=1, partial=None, sink=False):
     """Prompt-portion attention on the tcgen05 tensor cores (bfloat16, head size 64 or 128, heads per kv head a
     divisor of 128); see csrc/attention_prefill_tc.cu.  Arguments as `attention_prefill`.  `splits` > 1 cuts every
     CTA's keys into that many ranges that run side by side and are merged by a second kernel; `partial` is their
@@ -562,7 +566,8 @@ def attention_prefill_tc(q, k_pages, v_pages, segments, n_segments, n_tiles, slo
         _check(lib().lia_attention_prefill_tc(_p(q), _p(k_pages), _p(v_pages), _p(segments), n_segments, n_tiles,
                                               _p(slots), _p(block_table), block_table.shape[1], _p(out), nq, nkv, d,
                                               k_pages.shape[1], int(window or 0), scale, k_pages.shape[0], splits,
-                                              _p(partial) if splits > 1 else None, q.shape[0], _p(error_flag), _stream()),
+                                              _p(partial) if splits > 1 else None, q.shape[0], 1 if sink else 0,
+                                              _p(error_flag), _stream()),
                "attention_prefill_tc")
 
 
@@ -965,3 +970,31 @@ def gemm_simt_batched(mode, a, w, out, alpha: float = 1.0, label=None):
         _check(lib().lia_gemm_simt_batched(mode, _p(a), dtype_code(a.dtype), a.stride(1), a.stride(0), _p(w),
                                            dtype_code(w.dtype), w.stride(1), w.stride(0), _p(out), dtype_code(out.dtype),
                                            out.stride(1), out.stride(0), B, M, N, K, alpha, _stream()), "gemm_simt_batched")
+
+
+def latent_attention_accepts(rank: int, dr: int) -> bool:
+    """Whether the tensor-core kernel for attention in a latent's space takes these sizes (bfloat16)."""
+    return bool(lib().lia_latent_attention_accepts(int(rank), int(dr)))
+
+
+def latent_attention(q1, q2, latent_pages, part_pages, positions, slots, block_table, out, heads, window, scale, splits=1,
+                     partial=None, error_flag=None, label=None, work_bytes=0, work_flops=0):
+    """Attention in a latent's space on the tensor cores (bfloat16): q1 [heads, tokens, rank] with the latents, q2
+    [tokens, heads dr] with the rotated key parts, out [heads, tokens, rank]; see csrc/latent_attention_mma.cu.
+    `splits` > 1 cuts every token's keys into that many ranges; `partial` is their 32-bit scratch of
+    splits * heads * tokens * (rank + 2) words."""
+    _cuda(q1, q2, latent_pages, part_pages, positions, slots, block_table, out, partial, error_flag)
+    if not (q1.dtype == q2.dtype == latent_pages.dtype == part_pages.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("latent_attention is a bfloat16 kernel")
+    rank, dr = latent_pages.shape[-1], part_pages.shape[-1]
+    n = q2.shape[0]
+    splits = int(splits)
+    if tuple(q1.shape) != (heads, n, rank) or tuple(out.shape) != (heads, n, rank) or q2.shape[1] != heads * dr:
+        raise KernelError("latent_attention: q1 and out are [heads, tokens, rank], q2 [tokens, heads dr]")
+    if splits > 1 and (partial is None or partial.dtype != torch.float32 or partial.numel() < splits * heads * n * (rank + 2)):
+        raise KernelError("latent_attention: the ranges need 32-bit scratch of splits * heads * tokens * (rank + 2) words")
+    with _timed("latent_attention", label, work_bytes, work_flops):
+        _check(lib().lia_latent_attention(_p(q1), _p(q2), _p(latent_pages), _p(part_pages), _p(positions), _p(slots),
+                                          _p(block_table), block_table.shape[1], _p(out), _p(partial) if splits > 1 else None,
+                                          n, heads, rank, dr, latent_pages.shape[1], int(window or 0), scale,
+                                          latent_pages.shape[0], splits, _p(error_flag), _stream()), "latent_attention")

@@ -126,7 +126,7 @@ class DecoderModel:
         device = runtime.device
 
         def on_device(names):
-            return {n: tensors[n].to(device) for n in names}
+            return {n: tensors[n].to(device) for n in names if n in tensors}      # (an optional tensor may be absent)
 
         table = tensors[spec.embedding_name].to(device)
         self.embedding = prepare_weight(table, runtime)

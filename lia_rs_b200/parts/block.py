@@ -137,7 +137,14 @@ class SandwichBlock(Arrangement):
 
     @staticmethod
     def tensor_specs(spec: LayerSpec, prefix: str) -> list:
-        return [t for cls, params, place in SandwichBlock._classes(spec) for t in cls.tensor_specs(params, prefix + spec.names[place])]
+        specs = [t for cls, params, place in SandwichBlock._classes(spec) for t in cls.tensor_specs(params, prefix + spec.names[place])]
+        if spec.feed_forward is None:
+            # a checkpoint may carry the norms of the absent sublayer all the same: taken if there, never used
+            for place in SandwichBlock.PLACES[2:]:
+                norm = spec.norm_at(place)
+                specs += [TensorSpec(t.name, t.shape, t.kind, optional=True)
+                          for t in lookup(NORMS, norm.kind, "norm").tensor_specs(norm.params, prefix + spec.names[place])]
+        return specs
 
     def __init__(self, spec: LayerSpec, tensors: dict, prefix: str, runtime):
         self.runtime = runtime

@@ -36,15 +36,20 @@ class PagedAttention:
                              f"most {ops.ATTENTION_HEAD_DIM_MAX} (what the attention kernels take)")
 
     def __init__(self, dtype: torch.dtype, heads: int, kv_heads: int, head_dim: int, window, scale: float,
-                 rotate_half=None):
+                 rotate_half=None, sink: bool = False):
         """`rotate_half`: what the mixer's position encoding answers to `rotate_half()`; with it (and the
         tensor variant, and at most 16 query heads per kv head) decode-only steps encode, append and attend in
-        one kernel (`forward_fused`)."""
+        one kernel (`forward_fused`).  `sink`: one is added to the softmax's denominator (the weight of a key of score 0
+        that has no value); the tensor variant's kernels take it, the kernel for every size behind this class does not
+        (`ops.attention_general` does)."""
         self.check(heads, kv_heads, head_dim)
+        self.sink = bool(sink)
         self.nq, self.nkv, self.d = int(heads), int(kv_heads), int(head_dim)
         self.window, self.scale = window, float(scale)
         self.group = self.nq // self.nkv
         self.variant = "tensor" if dtype == torch.bfloat16 and self.d in ops.DECODE_HEAD_DIMS else "generic"
+        if self.sink and (self.variant != "tensor" or self.nq // self.nkv > 64):
+            raise ValueError("attention with a sink: only the tensor-core kernels behind this class take one")
         if dtype == torch.bfloat16 and self.variant == "generic" and self.d not in _told:
             _told.add(self.d)
             print(f"[lia_rs_b200] bfloat16 attention with head size {self.d} runs on the kernel for every size "
@@ -165,7 +170,7 @@ class PagedAttention:
                         more = dict(splits=splits, partial=ctx.runtime.scratch("attn.prefill_partial", words, torch.float32))
                 kernel(q, kv.k_pages, kv.v_pages, ctx.prefill_segments, ctx.n_prefill_segments, tiles, ctx.slots,
                        kv.block_table, out, nq, nkv, d, self.window, self.scale, ctx.error_flag, work_flops=work_flops,
-                       **more)
+                       sink=self.sink, **more)
             else:
                 ops.attention_generic(q, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table, out, nq, nkv,
                                       d, self.window, self.scale, rows=ctx.prefill_rows, error_flag=ctx.error_flag)
@@ -175,7 +180,7 @@ class PagedAttention:
         partial, counters = (None, None) if clustered else self._decode_scratch(ctx, n_rows, n_splits)
         ops.attention_decode(q, kv.k_pages, kv.v_pages, rows, ctx.positions, ctx.slots, kv.block_table, out, partial,
                              self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
-                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered, all_new=all_new)
+                             error_flag=ctx.error_flag, work_bytes=work_bytes, cluster=clustered, all_new=all_new, sink=self.sink)
 
     def forward_fused(self, ctx, qkv, kv, out) -> bool:
         """For a step of single decoded tokens and a rotate-half (or no) position encoding: encoding of q and k,
@@ -189,5 +194,6 @@ class PagedAttention:
         ops.attention_decode(None, kv.k_pages, kv.v_pages, ctx.decode_rows, ctx.positions, ctx.slots, kv.block_table,
                              out, partial, self.nq, self.nkv, self.d, self.window, self.scale, 0, n_splits, counters,
                              qkv=qkv, inv_freq=inv_freq, rotary_dim=rotary_dim, write_kv=kv.writes,
-                             error_flag=ctx.error_flag, label="fused", work_bytes=self._work(ctx, 2)[0], cluster=clustered)
+                             error_flag=ctx.error_flag, label="fused", work_bytes=self._work(ctx, 2)[0], cluster=clustered,
+                             sink=self.sink)
         return True

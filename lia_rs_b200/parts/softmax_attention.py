@@ -33,6 +33,7 @@ from ..kernels import ops
 from ..weights import TensorSpec
 from .base import DeferredNorm, KVCacheRequest, Mixer, NORMS, lookup, register_mixer
 from .linear import ACCUM, STORE, linear, prepare_weight
+from .paged_attention import PagedAttention
 from .rotary import band_scaled_frequencies
 
 
@@ -63,9 +64,6 @@ class SinkAttention(Mixer):
     takes_deferred_norm = True
     NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "o_bias": "o.b",
              "q_norm": "q.norm", "k_norm": "k.norm", "mix": "vmix"}
-
-    def graph_key(self, ctx) -> tuple:
-        return ()
 
     @staticmethod
     def _names(params, prefix):
@@ -131,6 +129,15 @@ class SinkAttention(Mixer):
         self.rot_dims, self.freq = _frequencies(params.get("rot"), device)
         self.mix_mode = {None: 0, "source": 1, "mixed": 2}[params.get("value_mix")]
         self.mix_lambda = float(tensors[n["mix"]].to(torch.float32)) if self.mix_mode == 2 else 0.0
+        # bfloat16 with keys and values of one head size that the tensor-core kernels take: those kernels; else the
+        # kernel for every size
+        self.paged = None
+        if runtime.compute_dtype == torch.bfloat16 and self.d == self.dv and self.d in ops.DECODE_HEAD_DIMS and \
+                self.nq // self.nkv <= 64:
+            self.paged = PagedAttention(runtime.compute_dtype, self.nq, self.nkv, self.d, self.window, self.scale, sink=self.sink)
+
+    def graph_key(self, ctx) -> tuple:
+        return self.paged.graph_key(ctx) if self.paged is not None else ()
 
     def forward(self, ctx, x, residual, scale, kv=None, state=None):
         rt, n = self.runtime, x.shape[0]
@@ -144,9 +151,12 @@ class SinkAttention(Mixer):
                         self.mix_mode, self.mix_lambda, v_first, ctx.positions, ctx.slots, kv.block_table, q, kv.k_pages,
                         kv.v_pages, nq, nkv, d, dv, write_kv=kv.writes, error_flag=flag)
         o = ctx.buffer("sinkattn.o", (n, nq * dv), rt.compute_dtype)
-        ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, dv, dv, ctx.positions, ctx.slots,
-                              kv.block_table, o, (nq * dv, dv), n, nq, nkv, self.window, self.scale, sink=self.sink,
-                              error_flag=flag)
+        if self.paged is not None:
+            self.paged.forward(ctx, q, kv, o)
+        else:
+            ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, dv, dv, ctx.positions, ctx.slots,
+                                  kv.block_table, o, (nq * dv, dv), n, nq, nkv, self.window, self.scale, sink=self.sink,
+                                  error_flag=flag)
         linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
 
 
@@ -211,6 +221,24 @@ class LatentAttention(Mixer):
         self.q_norm = lookup(NORMS, "rmsnorm", "norm")(norm_params, {n["q_norm"]: tensors[n["q_norm"]]}, n["q_norm"], runtime)
         self.kv_norm = tensors[n["kv_norm"]].to(torch.float32).contiguous()
         self.rot_dims, self.freq = _frequencies(params.get("rot"), runtime.device)
+        self.tensor_cores = runtime.compute_dtype == torch.bfloat16 and ops.latent_attention_accepts(self.rank, self.dr)
+
+    def _splits(self, ctx, n: int) -> int:
+        """Into how many ranges the tensor-core kernel cuts each token's keys: as many as give every SM two CTAs, none
+        shorter than four tiles of 32 keys at the step's context bucket and window, at most 16.  It depends on the number
+        of rows and the context bucket alone, as a captured step needs."""
+        longest = min(ctx.context_bucket, self.window or ctx.context_bucket)
+        ctas = max(1, n * ((self.heads + 15) // 16))
+        return max(1, min(2 * ctx.runtime.sm_count // ctas, 16, longest // 128))
+
+    def _work(self, ctx):
+        """(cache bytes the single tokens read, flops of the prompt portions), for the profile only."""
+        if ops._profiler is None:
+            return 0, 0
+        seen = lambda p: min(p + 1, self.window or p + 1)
+        keys = sum(seen(start) for _, start, count, _ in ctx.segments if count == 1)
+        pairs = sum(seen(start + i) for _, start, count, _ in ctx.segments if count > 1 for i in range(count))
+        return keys * (self.rank + self.dr) * 2, 2 * self.heads * (2 * self.rank + self.dr) * pairs
 
     def _head_products(self, mode, a, w, out, name):
         """out[h] (op)= a[h] @ w[h]^T for every head (3-D tensors, a head a plane)."""
@@ -236,9 +264,17 @@ class LatentAttention(Mixer):
         q_absorbed = scratch("latent.q_absorbed", H * n * rank, dtype).view(H, n, rank)
         self._head_products(STORE, q_plain, self.w_k_up_t, q_absorbed, "k_up")
         mixed = scratch("latent.mixed", H * n * rank, dtype).view(H, n, rank)
-        ops.attention_general(q_absorbed, (rank, n * rank), q_rotated, (H * dr, dr), kv.k_pages, kv.v_pages, kv.k_pages,
-                              rank, rank, ctx.positions, ctx.slots, kv.block_table, mixed, (rank, n * rank), n, H, 1,
-                              self.window, self.scale, sink=False, error_flag=flag)
+        if self.tensor_cores:
+            splits = self._splits(ctx, n)
+            partial = scratch("latent.partial", splits * H * n * (rank + 2), torch.float32) if splits > 1 else None
+            work_bytes, work_flops = self._work(ctx)
+            ops.latent_attention(q_absorbed, q_rotated, kv.k_pages, kv.v_pages, ctx.positions, ctx.slots, kv.block_table,
+                                 mixed, H, self.window, self.scale, splits=splits, partial=partial, error_flag=flag,
+                                 work_bytes=work_bytes, work_flops=work_flops)
+        else:
+            ops.attention_general(q_absorbed, (rank, n * rank), q_rotated, (H * dr, dr), kv.k_pages, kv.v_pages, kv.k_pages,
+                                  rank, rank, ctx.positions, ctx.slots, kv.block_table, mixed, (rank, n * rank), n, H, 1,
+                                  self.window, self.scale, sink=False, error_flag=flag)
         o = ctx.buffer("latent.o", (n, H * dv), dtype)
         self._head_products(STORE, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
         linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

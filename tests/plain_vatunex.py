@@ -211,3 +211,15 @@ def forward(config, weights, tokens, return_layers=False):
         after.append(x.clone())
     logits = norm_one_plus(x, weights["final.norm"], eps) @ weights["head"].to(F64).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def greedy(config, weights, prompt, count):
+    """`count` tokens after `prompt`, each the largest logit's id (the largest id among equals)."""
+    tokens, out = list(prompt), []
+    for _ in range(count):
+        row = forward(config, weights, tokens)[-1]
+        best = row.max()
+        token = max(i for i in range(len(row)) if row[i] == best)
+        out.append(token)
+        tokens.append(token)
+    return out
