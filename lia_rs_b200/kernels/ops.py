@@ -112,7 +112,8 @@ class _Signatures:
                              c_int, c_void_p]
     lia_selective_scan = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_void_p,
                           c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_void_p]
+                          c_void_p, c_int, c_int, c_int, c_int, c_void_p, ctypes.c_longlong, c_void_p]
+    lia_selective_scan_chunk_floats = [c_int, c_int, c_int, c_int]
     lia_gemm_simt_batched = [c_int, c_void_p, c_int, c_int, ctypes.c_longlong, c_void_p, c_int, c_int, ctypes.c_longlong,
                              c_void_p, c_int, c_int, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p]
 
@@ -938,11 +939,21 @@ def conv_state_update(x, state, positions, slots, channels: int):
                                            x.shape[0], channels, taps, _stream()), "conv_state_update")
 
 
-def selective_scan(x, dt_raw, dt_bias, A, bc, b_offset, c_offset, D, z, state, segments, n_segments, single_rows, slots, out):
+def selective_scan_chunk_floats(n_tokens: int, n_segments: int, channels: int, states: int) -> int:
+    """Words of 32-bit scratch with which `selective_scan` cuts a step's portions into chunks that run side by side."""
+    fn = lib().lia_selective_scan_chunk_floats
+    fn.restype = ctypes.c_longlong
+    return int(fn(int(n_tokens), int(n_segments), int(channels), int(states)))
+
+
+def selective_scan(x, dt_raw, dt_bias, A, bc, b_offset, c_offset, D, z, state, segments, n_segments, single_rows, slots, out,
+                   chunk_scratch=None):
     """The recurrence S <- exp(dt A) S + dt x B, y = (S C + D x) silu(z) with dt = softplus(dt_raw + dt_bias), along the
-    step's runs (`segments` [n, 3] and `single_rows`), state [slots, channels, states] 32-bit; see csrc/selective_scan.cu."""
-    _cuda(x, dt_raw, dt_bias, A, D, segments, single_rows, slots, out)
-    _f32(x, dt_raw, dt_bias, A, bc, D, z, state)
+    step's runs (`segments` [n, 3] and `single_rows`), state [slots, channels, states] 32-bit; see csrc/selective_scan.cu.
+    With `chunk_scratch` (32-bit, `selective_scan_chunk_floats` words) the portions are cut into chunks of 64 tokens that
+    run side by side: a pass from zero states, a carry along each portion, a pass from the true start states."""
+    _cuda(x, dt_raw, dt_bias, A, D, segments, single_rows, slots, out, chunk_scratch)
+    _f32(x, dt_raw, dt_bias, A, bc, D, z, state, chunk_scratch)
     n, channels = x.shape
     states = A.shape[1]
     n_single = 0 if single_rows is None else single_rows.numel()
@@ -953,7 +964,8 @@ def selective_scan(x, dt_raw, dt_bias, A, bc, b_offset, c_offset, D, z, state, s
         _check(lib().lia_selective_scan(_p(x), _p(dt_raw), _p(dt_bias), _p(A), _p(bc), bc.stride(0), int(b_offset),
                                         int(c_offset), _p(D), _p(z), z.stride(0), _p(state), state.stride(0), _p(segments), int(n_segments),
                                         _p(single_rows), n_single, _p(slots), _p(out), dtype_code(out.dtype), channels,
-                                        states, _stream()), "selective_scan")
+                                        states, n, _p(chunk_scratch), 0 if chunk_scratch is None else chunk_scratch.numel(),
+                                        _stream()), "selective_scan")
 
 
 def gemm_simt_batched(mode, a, w, out, alpha: float = 1.0, label=None):

@@ -10,7 +10,9 @@
 What a request carries from token to token is one 32-bit state per slot: the convolution's last taps - 1 inputs and
 S.  The products may run in the compute element type; the convolution and its activation, step sizes, decays,
 exponentials, the state and the sums over it are 32-bit (csrc/selective_scan.cu).  A step's runs (prompt portions and
-single tokens) are walked token by token on the device, so a portion cut anywhere continues from the slot's state.
+single tokens) are walked token by token on the device, so a portion cut anywhere continues from the slot's state.  In a
+step of many tokens the portions are cut into chunks of 64 tokens that run side by side: the recurrence is linear in the
+state, so a chunk's end state is its end state from zero plus the decayed state it started from.
 
 Parameters: hidden, inner, state, dt_rank, taps, and optionally `names` (checkpoint names behind the part's prefix)."""
 from __future__ import annotations
@@ -27,6 +29,7 @@ from .linear import ACCUM, STORE, linear, prepare_weight
 class SelectiveScan(Mixer):
     graph_safe = True
     takes_deferred_norm = True
+    CHUNKED_FROM = 256        # tokens of a step from which its portions are cut into chunks that run side by side
     NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "x": "x", "dt": "dt", "dt_bias": "dt.b", "A_log": "A_log",
              "D": "D", "o": "o"}
 
@@ -98,6 +101,11 @@ class SelectiveScan(Mixer):
         dt_raw = ctx.buffer("scan.dt", (n, inner), torch.float32)
         linear(rt, STORE, low, self.w_dt, dt_raw, error_flag=flag, name="dt")
         y = ctx.buffer("scan.y", (n, inner), dtype)
+        chunk_scratch = None
+        if ctx.n_prefill_segments and n >= self.CHUNKED_FROM:
+            words = ops.selective_scan_chunk_floats(n, ctx.n_prefill_segments, inner, states)
+            chunk_scratch = ctx.runtime.scratch("scan.chunks", words, torch.float32)
         ops.selective_scan(u, dt_raw, self.dt_bias, self.decay, projected, rank, rank + states, self.skip, uz[:, inner:],
-                           scan_state, ctx.prefill_segments, ctx.n_prefill_segments, ctx.decode_rows, ctx.slots, y)
+                           scan_state, ctx.prefill_segments, ctx.n_prefill_segments, ctx.decode_rows, ctx.slots, y,
+                           chunk_scratch=chunk_scratch)
         linear(rt, ACCUM, y, self.w_o, residual, scale, error_flag=flag, name="o")

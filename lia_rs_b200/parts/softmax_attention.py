@@ -240,9 +240,17 @@ class LatentAttention(Mixer):
         pairs = sum(seen(start + i) for _, start, count, _ in ctx.segments if count > 1 for i in range(count))
         return keys * (self.rank + self.dr) * 2, 2 * self.heads * (2 * self.rank + self.dr) * pairs
 
-    def _head_products(self, mode, a, w, out, name):
-        """out[h] (op)= a[h] @ w[h]^T for every head (3-D tensors, a head a plane)."""
-        ops.gemm_simt_batched(mode, a, w, out, label=name)
+    HEADS_ONE_BY_ONE_FROM = 256       # tokens from which a head's product goes to the tensor cores by itself
+
+    def _head_products(self, ctx, a, w, out, name):
+        """out[h] = a[h] @ w[h]^T for every head (3-D tensors, a head a plane).  Few tokens: all heads in one launch on
+        the 32-bit pipes (the matrices are small and read once).  Many tokens in bfloat16: a product per head through
+        `linear`, which takes it to the tensor cores."""
+        if a.dtype == torch.bfloat16 and a.shape[1] >= self.HEADS_ONE_BY_ONE_FROM and ops.gemm_tc_accepts(STORE, a[0], w[0], out[0]):
+            for h in range(a.shape[0]):
+                linear(self.runtime, STORE, a[h], w[h], out[h], error_flag=ctx.error_flag, name=name)
+        else:
+            ops.gemm_simt_batched(STORE, a, w, out, label=name)
 
     def forward(self, ctx, x, residual, scale, kv=None, state=None):
         rt, n = self.runtime, x.shape[0]
@@ -262,7 +270,7 @@ class LatentAttention(Mixer):
                            kv.block_table, q_plain, q_rotated, kv.k_pages, kv.v_pages, H, d, dr, rank, write_kv=kv.writes,
                            error_flag=flag)
         q_absorbed = scratch("latent.q_absorbed", H * n * rank, dtype).view(H, n, rank)
-        self._head_products(STORE, q_plain, self.w_k_up_t, q_absorbed, "k_up")
+        self._head_products(ctx, q_plain, self.w_k_up_t, q_absorbed, "k_up")
         mixed = scratch("latent.mixed", H * n * rank, dtype).view(H, n, rank)
         if self.tensor_cores:
             splits = self._splits(ctx, n)
@@ -276,5 +284,5 @@ class LatentAttention(Mixer):
                                   rank, rank, ctx.positions, ctx.slots, kv.block_table, mixed, (rank, n * rank), n, H, 1,
                                   self.window, self.scale, sink=False, error_flag=flag)
         o = ctx.buffer("latent.o", (n, H * dv), dtype)
-        self._head_products(STORE, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
+        self._head_products(ctx, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
         linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

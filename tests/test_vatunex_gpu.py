@@ -145,6 +145,33 @@ def test_ways_of_cutting_agree_in_32_bit(models, name):
         assert np.abs(other - outputs[0]).max() <= 3e-5 * scale
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["vat-B", "vat-C", "vat-D"])
+def test_the_roads_of_long_steps_on_short_ones(models, name, dtype, monkeypatch):
+    """What only steps of hundreds of tokens do (the scan's portions cut into chunks that run side by side, a product per
+    head through `linear`), switched on from eight tokens: whole prompts and portions beside single tokens."""
+    from lia_rs_b200.parts.selective_scan import SelectiveScan
+    from lia_rs_b200.parts.softmax_attention import LatentAttention
+    monkeypatch.setattr(SelectiveScan, "CHUNKED_FROM", 8)
+    monkeypatch.setattr(LatentAttention, "HEADS_ONE_BY_ONE_FROM", 8)
+    model = models[name]
+    tokens, other = tokens_of(model, 171, 91), tokens_of(model, 40, 92)
+    reference, reference_other = vh.plain_logits(model, tokens), vh.plain_logits(model, other)
+    engine = make_engine(model, dtype, 256)
+    replay = helpers.Replayer(engine)
+    logits = replay.step([("w", tokens, range(len(tokens)))], end=["w"])
+    vh.assert_close(logits, reference, dtype, f"{name} whole, long roads", model["config"])
+    rows, others = [], []
+    out = replay.step([("r", tokens[:70], range(70)), ("o", other[:1], [0])])
+    rows.append(out[:70]); others.append(out[70:])
+    out = replay.step([("o", other[1:2], [0]), ("r", tokens[70:], range(101))])
+    rows.append(out[1:]); others.append(out[:1])
+    out = replay.step([("o", other[2:], range(38))])
+    others.append(out)
+    vh.assert_close(np.concatenate(rows), reference, dtype, f"{name} portions, long roads", model["config"])
+    vh.assert_close(np.concatenate(others), reference_other, dtype, f"{name} beside them, long roads", model["config"])
+
+
 @pytest.mark.parametrize("name", ["vat-B", "vat-C"])
 def test_long_decoding(models, name):
     """400 tokens one by one behind a short prompt, bfloat16: state, windows and pages hold over hundreds of steps."""

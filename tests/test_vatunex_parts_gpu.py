@@ -287,15 +287,18 @@ def test_causal_conv_carries_its_inputs_over_steps(taps):
         assert torch.allclose(rows, want[r][:rows.shape[0]], atol=2e-5, rtol=2e-5), (r, taps)
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("states", [3, 8, 16, 24, 40])
-def test_selective_scan_carries_its_state_over_steps(states):
+def test_selective_scan_carries_its_state_over_steps(states, chunked):
+    """Runs of 1 to 150 tokens of three requests on two slots; `chunked`: the portions are cut into chunks of 64 tokens
+    that run side by side (one, two and three chunks a portion, beside single tokens), with the same results."""
     from lia_rs_b200.kernels import ops
     g = torch.Generator().manual_seed(40 + states)
     channels, rank = 50, 3
     A = -(0.2 + 3 * torch.rand(channels, states, generator=g))
     D, dt_bias = torch.randn(channels, generator=g), torch.randn(channels, generator=g) - 1
     seqs = {}
-    for r, length in (("a", 40), ("b", 9), ("c", 21)):
+    for r, length in (("a", 230), ("b", 9), ("c", 133)):
         x, dt_raw, z = (torch.randn(length, channels, generator=g) for _ in range(3))
         bc = torch.randn(length, rank + 2 * states + 2, generator=g)
         dt = torch.nn.functional.softplus(dt_raw.to(F64) + dt_bias.to(F64))
@@ -303,7 +306,7 @@ def test_selective_scan_carries_its_state_over_steps(states):
         seqs[r] = dict(x=x, dt=dt_raw, z=z, bc=bc, want=y * (z.to(F64) * torch.sigmoid(z.to(F64))))
     state = torch.zeros(2, channels * states + 5, device="cuda")[:, 5:].view(2, channels, states)     # a view: a slot's stride is its own
     slot_of, at, got = {"a": 0, "b": 1}, {r: 0 for r in seqs}, {r: [] for r in seqs}
-    steps = [[("a", 4), ("b", 1)], [("b", 8), ("a", 1)], [("a", 1)], [("c", 2), ("a", 11)], [("a", 1), ("c", 1)], [("c", 18), ("a", 22)]]
+    steps = [[("a", 4), ("b", 1)], [("b", 8), ("a", 1)], [("a", 1)], [("c", 2), ("a", 150)], [("a", 1), ("c", 1)], [("c", 130), ("a", 73)]]
     for step in steps:
         if any(r == "c" for r, _ in step) and "c" not in slot_of:
             slot_of["c"] = 1
@@ -314,8 +317,11 @@ def test_selective_scan_carries_its_state_over_steps(states):
         x, dt, z, bc = cat("x"), cat("dt"), cat("z"), cat("bc")
         wide_z = torch.cat([torch.zeros_like(z), z], dim=1)                   # z as the second half of wider rows
         out = torch.empty(x.shape[0], channels, device="cuda")
+        scratch = None
+        if chunked and n_segments:
+            scratch = torch.full((ops.selective_scan_chunk_floats(x.shape[0], n_segments, channels, states),), float("nan"), device="cuda")
         ops.selective_scan(x, dt, dev(dt_bias), dev(A), bc, rank, rank + states, dev(D), wide_z[:, channels:], state, segments,
-                           n_segments, singles, slots, out)
+                           n_segments, singles, slots, out, chunk_scratch=scratch)
         row = 0
         for r, count in step:
             got[r].append(out[row:row + count].cpu())
@@ -323,7 +329,7 @@ def test_selective_scan_carries_its_state_over_steps(states):
             at[r] += count
     for r in ("a", "c"):
         rows = torch.cat(got[r]).to(F64)
-        assert torch.allclose(rows, seqs[r]["want"][:rows.shape[0]], atol=5e-5, rtol=5e-5), (r, states)
+        assert torch.allclose(rows, seqs[r]["want"][:rows.shape[0]], atol=1e-4, rtol=1e-4), (r, states, chunked)
 
 
 def test_products_of_many_heads_at_once():
