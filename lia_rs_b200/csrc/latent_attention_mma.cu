@@ -5,7 +5,8 @@
 // for the keys j of the token's own request with max(0, pos - window + 1) <= j <= pos.
 //
 // One CTA serves one token and up to 16 of its heads (the M of an m16n8k16 product) and walks the token's keys 32 at a
-// time: the tile's records come into shared memory once for all heads; warp w multiplies the queries with keys 8w..8w+7
+// time: the tile's records come into shared memory once for all heads, by asynchronous copies issued a tile ahead;
+// warp w multiplies the queries with keys 8w..8w+7
 // over all of rank + dr; the scores meet in shared memory; every warp takes the softmax of the 16 x 32 scores for itself
 // (32-bit, base 2, running maximum and sum per row) and multiplies the probabilities, rounded to bfloat16, with its own
 // quarter of the latent's columns, accumulating in 32-bit registers.  Prompt portions and single tokens are the same
@@ -62,9 +63,9 @@ latent_attention_kernel(LatentParams p) {
     extern __shared__ __align__(16) uint8_t latent_smem[];
     const int dk = p.rank + p.dr, ld = dk + PAD;
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(latent_smem);              // [16][ld]
-    __nv_bfloat16* ks = qs + 16 * ld;                                                 // [KEYS][ld]
-    float* ss = reinterpret_cast<float*>(ks + KEYS * ld);                             // [16][KEYS + 1]
-    int* key_rows = reinterpret_cast<int*>(ss + 16 * (KEYS + 1));                     // [KEYS]
+    __nv_bfloat16* ks_all = qs + 16 * ld;                                             // [2][KEYS][ld]: this tile and the next
+    float* ss = reinterpret_cast<float*>(ks_all + 2 * KEYS * ld);                     // [16][KEYS + 1]
+    int* key_rows_all = reinterpret_cast<int*>(ss + 16 * (KEYS + 1));                 // [2][KEYS]
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, h0 = blockIdx.y * 16;
@@ -97,24 +98,33 @@ latent_attention_kernel(LatentParams p) {
     float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
     const int col0 = warp * NT * 8;                          // this warp's columns of the latent
 
+    // Four threads bring one key's record: one look at the block table a thread and tile, 16-byte asynchronous copies
+    // that land while the tile before is multiplied.
+    auto fetch = [&](int tile, int buffer) {
+        const int r = tid >> 2, j = first + tile * KEYS + r;
+        const int row = j <= pos ? cache_row_of(table, j, p.page_size, -1, p.num_pages, p.error_flag) : -1;
+        if ((tid & 3) == 0) key_rows_all[buffer * KEYS + r] = row;
+        __nv_bfloat16* dst = ks_all + ((size_t)buffer * KEYS + r) * ld;
+        for (int c = (tid & 3) * 8; c < dk; c += 32) {
+            if (row >= 0) {
+                const __nv_bfloat16* src = c < p.rank ? p.latent_pages + (size_t)row * p.rank + c
+                                                      : p.part_pages + (size_t)row * p.dr + (c - p.rank);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst + c)), "l"(src) : "memory");
+            } else {
+                *reinterpret_cast<uint4*>(dst + c) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (tile_lo < tile_hi) fetch(tile_lo, 0);
+
     for (int tile = tile_lo; tile < tile_hi; ++tile) {
-        const int key0 = first + tile * KEYS;
-        __syncthreads();                                     // the tile before is used up (and, at first, the queries are there)
-        if (tid < KEYS) {
-            const int j = key0 + tid;
-            key_rows[tid] = j <= pos ? cache_row_of(table, j, p.page_size, -1, p.num_pages, p.error_flag) : -1;
-        }
-        __syncthreads();
-        for (int e = tid; e < KEYS * q_chunks; e += THREADS) {
-            const int r = e / q_chunks, c = (e % q_chunks) * 8;
-            const int row = key_rows[r];
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (row >= 0)
-                v = c < p.rank ? *reinterpret_cast<const uint4*>(p.latent_pages + (size_t)row * p.rank + c)
-                               : *reinterpret_cast<const uint4*>(p.part_pages + (size_t)row * p.dr + (c - p.rank));
-            *reinterpret_cast<uint4*>(ks + r * ld + c) = v;
-        }
-        __syncthreads();
+        const int buffer = (tile - tile_lo) & 1;
+        const __nv_bfloat16* ks = ks_all + (size_t)buffer * KEYS * ld;
+        const int* key_rows = key_rows_all + buffer * KEYS;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                     // this tile is there (at first: the queries too); the one before is used up
+        if (tile + 1 < tile_hi) fetch(tile + 1, buffer ^ 1);
         // ---- scores of keys 8 warp .. 8 warp + 7 for the 16 rows ----
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         {
@@ -248,7 +258,7 @@ __global__ void latent_merge_kernel(LatentParams p) {
 
 size_t latent_smem_bytes(int rank, int dr) {
     const size_t ld = (size_t)rank + dr + PAD;
-    return (16 + KEYS) * ld * 2 + 16 * (KEYS + 1) * sizeof(float) + KEYS * sizeof(int);
+    return (16 + 2 * KEYS) * ld * 2 + 16 * (KEYS + 1) * sizeof(float) + 2 * KEYS * sizeof(int);
 }
 
 template <int NT>

@@ -120,6 +120,8 @@ class _Signatures:
     lia_latent_attention_accepts = [c_int, c_int]
     lia_latent_attention = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
+    lia_gemm_mma_batched_accepts = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int]
+    lia_gemm_mma_batched = [c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_void_p, ctypes.c_longlong, ctypes.c_longlong, c_int, c_int, c_int, c_int, c_void_p]
 
 def dtype_code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
@@ -1010,3 +1012,32 @@ def latent_attention(q1, q2, latent_pages, part_pages, positions, slots, block_t
                                           _p(block_table), block_table.shape[1], _p(out), _p(partial) if splits > 1 else None,
                                           n, heads, rank, dr, latent_pages.shape[1], int(window or 0), scale,
                                           latent_pages.shape[0], splits, _p(error_flag), _stream()), "latent_attention")
+
+
+def _batched_arguments(a, w, out):
+    for t in (a, w, out):
+        if not t.is_cuda or t.dim() != 3 or t.stride(2) != 1:
+            raise KernelError("a batched product takes 3-D CUDA tensors with contiguous rows")
+    B, M, K = a.shape
+    N = out.shape[2]
+    if tuple(w.shape) != (B, N, K) or tuple(out.shape) != (B, M, N):
+        raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    return (_p(a), a.stride(1), a.stride(0), _p(w), w.stride(1), w.stride(0), _p(out), out.stride(1), out.stride(0)), (B, M, N, K)
+
+
+def gemm_mma_batched_accepts(a, w, out) -> bool:
+    """Whether the tensor-core kernel for many small products takes these tensors (bfloat16 [B, M, K], [B, N, K] ->
+    [B, M, N]): K and the operands' strides multiples of 8 elements, N and the output's strides even, aligned bases."""
+    if not (a.dtype == w.dtype == out.dtype == torch.bfloat16):
+        return False
+    pointers, (B, M, N, K) = _batched_arguments(a, w, out)
+    return bool(lib().lia_gemm_mma_batched_accepts(*pointers, M, N, K))
+
+
+def gemm_mma_batched(a, w, out, label=None):
+    """out[b] = a[b] @ w[b]^T for every b in one launch on the tensor cores (bfloat16); see csrc/gemm_mma_batched.cu."""
+    pointers, (B, M, N, K) = _batched_arguments(a, w, out)
+    if not (a.dtype == w.dtype == out.dtype == torch.bfloat16):
+        raise KernelError("gemm_mma_batched is a bfloat16 kernel")
+    with _timed("gemm_mma_batched", label, work=lambda: _gemm_work(a.reshape(-1, K), w.reshape(-1, K), out.reshape(-1, N))):
+        _check(lib().lia_gemm_mma_batched(*pointers, B, M, N, K, _stream()), "gemm_mma_batched")

@@ -172,6 +172,9 @@ class Mixer(Part):
     # A 32-bit vector [hidden] that belongs to the mixer's output (the bias of its last product) and that `forward` does
     # NOT add: the arrangement adds it where it next touches the output (an arrangement that cannot refuses the mixer).
     output_bias = None
+    # True: `forward` takes `store=True` and then WRITES scale * mixer(x) into `residual` instead of adding to it (its
+    # last product stores); an arrangement that gives the part a buffer of its own then need not clear it first.
+    can_store = False
 
     @staticmethod
     def cache_request(params: dict) -> Optional[KVCacheRequest]:
@@ -189,6 +192,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     takes_deferred_norm = False      # as for Mixer
+    can_store = False                # as for Mixer
 
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, scale: float):
         """residual += scale * feed_forward(x)."""

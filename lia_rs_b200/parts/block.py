@@ -172,8 +172,11 @@ class SandwichBlock(Arrangement):
         deferred = DeferredNorm(ctx, self.pre1, residual)
         x = deferred if self.mixer.takes_deferred_norm else deferred.tensor()
         y = ctx.buffer("block.sublayer", tuple(residual.shape), torch.float32)
-        y.zero_()
-        self.mixer.forward(ctx, x, y, 1.0, kv=kv, state=state)
+        if self.mixer.can_store:
+            self.mixer.forward(ctx, x, y, 1.0, kv=kv, state=state, store=True)
+        else:
+            y.zero_()
+            self.mixer.forward(ctx, x, y, 1.0, kv=kv, state=state)
         weight, eps = self.post["norm1b"]
         if self.feed_forward is None:
             ops.norm_residual(y, weight, residual, eps, bias=self.mixer.output_bias)
@@ -186,8 +189,11 @@ class SandwichBlock(Arrangement):
             x = ctx.buffer("block.x2", tuple(residual.shape), self.runtime.compute_dtype)
             ops.norm_residual(y, weight, residual, eps, bias=self.mixer.output_bias, next_weight=next_weight, next_out=x,
                               next_eps=next_eps)
-        y.zero_()
-        self.feed_forward.forward(ctx, x, y, 1.0)
+        if self.feed_forward.can_store:
+            self.feed_forward.forward(ctx, x, y, 1.0, store=True)
+        else:
+            y.zero_()
+            self.feed_forward.forward(ctx, x, y, 1.0)
         weight, eps = self.post["norm2b"]
         ops.norm_residual(y, weight, residual, eps)
         return None

@@ -57,6 +57,7 @@ class DenseActivation(FeedForward):
     down matrices behind the part's prefix."""
     graph_safe = True
     takes_deferred_norm = True
+    can_store = True
     NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
     ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "silu": 2}
 
@@ -89,10 +90,10 @@ class DenseActivation(FeedForward):
         self.w_up = prepare_weight(tensors[up], runtime)
         self.w_down = prepare_weight(tensors[down], runtime)
 
-    def forward(self, ctx, x, residual, scale):
+    def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
         up = ctx.buffer("ffn.up", (n, self.intermediate), torch.float32)
         linear(rt, STORE, x, self.w_up, up, error_flag=ctx.error_flag, name="up")
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
         rt.ops.activation_rows(up, act, self.activation)
-        linear(rt, ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")
+        linear(rt, STORE if store else ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")

@@ -29,6 +29,7 @@ from .linear import ACCUM, STORE, linear, prepare_weight
 class SelectiveScan(Mixer):
     graph_safe = True
     takes_deferred_norm = True
+    can_store = True
     CHUNKED_FROM = 256        # tokens of a step from which its portions are cut into chunks that run side by side
     NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "x": "x", "dt": "dt", "dt_bias": "dt.b", "A_log": "A_log",
              "D": "D", "o": "o"}
@@ -79,7 +80,7 @@ class SelectiveScan(Mixer):
         self.dt_bias, self.skip = f32(tensors[n["dt_bias"]]), f32(tensors[n["D"]])
         self.decay = (-torch.exp(tensors[n["A_log"]].to(torch.float32))).contiguous()
 
-    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+    def forward(self, ctx, x, residual, scale, kv=None, state=None, store=False):
         rt, n = self.runtime, x.shape[0]
         inner, states, rank, taps = self.inner, self.states, self.rank, self.taps
         flag, dtype = ctx.error_flag, rt.compute_dtype
@@ -108,4 +109,4 @@ class SelectiveScan(Mixer):
         ops.selective_scan(u, dt_raw, self.dt_bias, self.decay, projected, rank, rank + states, self.skip, uz[:, inner:],
                            scan_state, ctx.prefill_segments, ctx.n_prefill_segments, ctx.decode_rows, ctx.slots, y,
                            chunk_scratch=chunk_scratch)
-        linear(rt, ACCUM, y, self.w_o, residual, scale, error_flag=flag, name="o")
+        linear(rt, STORE if store else ACCUM, y, self.w_o, residual, scale, error_flag=flag, name="o")

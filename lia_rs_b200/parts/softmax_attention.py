@@ -62,6 +62,7 @@ def _check_rot(rot, limit, what):
 class SinkAttention(Mixer):
     graph_safe = True
     takes_deferred_norm = True
+    can_store = True
     NAMES = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b", "o_bias": "o.b",
              "q_norm": "q.norm", "k_norm": "k.norm", "mix": "vmix"}
 
@@ -139,7 +140,7 @@ class SinkAttention(Mixer):
     def graph_key(self, ctx) -> tuple:
         return self.paged.graph_key(ctx) if self.paged is not None else ()
 
-    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+    def forward(self, ctx, x, residual, scale, kv=None, state=None, store=False):
         rt, n = self.runtime, x.shape[0]
         nq, nkv, d, dv = self.nq, self.nkv, self.d, self.dv
         flag = ctx.error_flag
@@ -157,13 +158,14 @@ class SinkAttention(Mixer):
             ops.attention_general(q, (nq * d, d), None, None, kv.k_pages, None, kv.v_pages, dv, dv, ctx.positions, ctx.slots,
                                   kv.block_table, o, (nq * dv, dv), n, nq, nkv, self.window, self.scale, sink=self.sink,
                                   error_flag=flag)
-        linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+        linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
 
 
 @register_mixer("latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
     takes_deferred_norm = True
+    can_store = True
     NAMES = {"q_down": "dq", "q_norm": "dq.norm", "q_up": "uq", "kv_down": "dkv", "kv_norm": "dkv.norm", "k_up": "uk",
              "v_up": "uv", "o": "o"}
 
@@ -240,19 +242,18 @@ class LatentAttention(Mixer):
         pairs = sum(seen(start + i) for _, start, count, _ in ctx.segments if count > 1 for i in range(count))
         return keys * (self.rank + self.dr) * 2, 2 * self.heads * (2 * self.rank + self.dr) * pairs
 
-    HEADS_ONE_BY_ONE_FROM = 256       # tokens from which a head's product goes to the tensor cores by itself
+    TENSOR_CORES_FROM = 32            # tokens from which the heads' products go to the tensor cores
 
     def _head_products(self, ctx, a, w, out, name):
-        """out[h] = a[h] @ w[h]^T for every head (3-D tensors, a head a plane).  Few tokens: all heads in one launch on
-        the 32-bit pipes (the matrices are small and read once).  Many tokens in bfloat16: a product per head through
-        `linear`, which takes it to the tensor cores."""
-        if a.dtype == torch.bfloat16 and a.shape[1] >= self.HEADS_ONE_BY_ONE_FROM and ops.gemm_tc_accepts(STORE, a[0], w[0], out[0]):
-            for h in range(a.shape[0]):
-                linear(self.runtime, STORE, a[h], w[h], out[h], error_flag=ctx.error_flag, name=name)
+        """out[h] = a[h] @ w[h]^T for every head (3-D tensors, a head a plane), all heads in one launch.  Few tokens, or
+        the 32-bit path: on the 32-bit pipes (the matrices are small and read once).  Many tokens in bfloat16: on the
+        tensor cores (csrc/gemm_mma_batched.cu) where that kernel takes the sizes."""
+        if a.dtype == torch.bfloat16 and a.shape[1] >= self.TENSOR_CORES_FROM and ops.gemm_mma_batched_accepts(a, w, out):
+            ops.gemm_mma_batched(a, w, out, label=name)
         else:
             ops.gemm_simt_batched(STORE, a, w, out, label=name)
 
-    def forward(self, ctx, x, residual, scale, kv=None, state=None):
+    def forward(self, ctx, x, residual, scale, kv=None, state=None, store=False):
         rt, n = self.runtime, x.shape[0]
         H, d, dr, dv, rank = self.heads, self.d, self.dr, self.dv, self.rank
         flag, dtype = ctx.error_flag, rt.compute_dtype
@@ -285,4 +286,4 @@ class LatentAttention(Mixer):
                                   self.window, self.scale, sink=False, error_flag=flag)
         o = ctx.buffer("latent.o", (n, H * dv), dtype)
         self._head_products(ctx, mixed, self.w_v_up, o.view(n, H, dv).transpose(0, 1), "v_up")
-        linear(rt, ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")
+        linear(rt, STORE if store else ACCUM, o, self.w_o, residual, scale, error_flag=flag, name="o")

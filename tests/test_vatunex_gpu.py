@@ -148,12 +148,12 @@ def test_ways_of_cutting_agree_in_32_bit(models, name):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["vat-B", "vat-C", "vat-D"])
 def test_the_roads_of_long_steps_on_short_ones(models, name, dtype, monkeypatch):
-    """What only steps of hundreds of tokens do (the scan's portions cut into chunks that run side by side, a product per
-    head through `linear`), switched on from eight tokens: whole prompts and portions beside single tokens."""
+    """What only steps of hundreds of tokens do (the scan's portions cut into chunks that run side by side, the heads'
+    products on the tensor cores), switched on from a few tokens: whole prompts and portions beside single tokens."""
     from lia_rs_b200.parts.selective_scan import SelectiveScan
     from lia_rs_b200.parts.softmax_attention import LatentAttention
     monkeypatch.setattr(SelectiveScan, "CHUNKED_FROM", 8)
-    monkeypatch.setattr(LatentAttention, "HEADS_ONE_BY_ONE_FROM", 8)
+    monkeypatch.setattr(LatentAttention, "TENSOR_CORES_FROM", 2)
     model = models[name]
     tokens, other = tokens_of(model, 171, 91), tokens_of(model, 40, 92)
     reference, reference_other = vh.plain_logits(model, tokens), vh.plain_logits(model, other)

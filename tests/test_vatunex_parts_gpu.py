@@ -344,3 +344,21 @@ def test_products_of_many_heads_at_once():
     half = torch.zeros(B, M, N, dtype=torch.bfloat16, device="cuda")
     ops.gemm_simt_batched(ops.GEMM_STORE, dev(a, torch.bfloat16), dev(w, torch.bfloat16), half)
     assert torch.allclose(half.float().cpu().to(F64), want, atol=0.15, rtol=3e-2)
+
+
+@pytest.mark.parametrize("B,M,N,K", [(3, 37, 24, 40), (16, 300, 128, 64), (2, 129, 66, 8), (5, 1, 512, 128)])
+def test_products_of_many_heads_on_the_tensor_cores(B, M, N, K):
+    """Sizes that are no multiples of the kernel's tiles, K shorter than and not a multiple of a step, outputs side by
+    side in a row and as planes."""
+    from lia_rs_b200.kernels import ops
+    g = torch.Generator().manual_seed(51)
+    a, w = torch.randn(B, M, K, generator=g).to(torch.bfloat16), torch.randn(B, N, K, generator=g).to(torch.bfloat16)
+    want = torch.einsum("bmk,bnk->bmn", a.to(F64), w.to(F64))
+    planes = torch.zeros(B, M, N, dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_mma_batched_accepts(dev(a), dev(w), planes)
+    ops.gemm_mma_batched(dev(a), dev(w), planes)
+    assert torch.allclose(planes.float().cpu().to(F64), want, atol=0.02 * K ** 0.5, rtol=1e-2)
+    side_by_side = torch.zeros(M, B * N, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_mma_batched(dev(a), dev(w), side_by_side.view(M, B, N).transpose(0, 1))
+    assert torch.equal(side_by_side.view(M, B, N).transpose(0, 1), planes)
+    assert not ops.gemm_mma_batched_accepts(dev(a)[:, :, :K - 1], dev(w)[:, :, :K - 1], planes)      # K no multiple of 8
