@@ -49,7 +49,7 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, long long ld, co
     const int pos = positions[t];
     const int m = run_before(positions, slots, t, slot, pos, taps - 1);
     const float* own = state + (size_t)slot * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float y = bias ? bias[c] : 0.f;
         for (int j = 0; j < taps - 1; ++j)
             y = fmaf(taps_weight[(size_t)c * taps + j], input_before(x, ld, own, channels, taps, t, pos, m, taps - 1 - j, c), y);
@@ -73,7 +73,7 @@ __global__ void conv_state_update_kernel(const float* __restrict__ x, long long 
     if (t + 1 < n_tokens && slots[t + 1] == slot && positions[t + 1] == pos + 1) return;      // not the run's last row
     const int m = run_before(positions, slots, t, slot, pos, taps - 1);
     float* own = state + (size_t)slot * state_stride;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float kept[MAX_TAPS];
 #pragma unroll
         for (int i = 0; i < MAX_TAPS - 1; ++i) {
@@ -278,12 +278,14 @@ LIA_EXPORT int lia_causal_conv(const float* x, long long ld, const float* taps_w
     if (n_tokens <= 0) return LIA_OK;
     if (channels <= 0 || taps < 1 || taps > MAX_TAPS || ld < channels || (taps > 1 && !state) || act < 0 || act > 1)
         return LIA_ERR_SIZE;
-    const int threads = channels >= 1024 ? 256 : 128;
+    const int threads = 128;
+    // few tokens: a token's channels over several CTAs, so that the step's rows fill the device
+    const dim3 grid(n_tokens, n_tokens >= 512 ? 1 : min(16, (channels + threads - 1) / threads));
     if (!out_copy || copy_dtype == LIA_F32)
-        return lia_launch(causal_conv_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, x, ld, taps_weight, bias,
+        return lia_launch(causal_conv_kernel<float>, grid, dim3(threads), 0, stream, x, ld, taps_weight, bias,
                           state, state_stride, positions, slots, out, (float*)out_copy, n_tokens, channels, taps, act);
     if (copy_dtype == LIA_BF16)
-        return lia_launch(causal_conv_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, x, ld, taps_weight,
+        return lia_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, ld, taps_weight,
                           bias, state, state_stride, positions, slots, out, (__nv_bfloat16*)out_copy, n_tokens, channels,
                           taps, act);
     return LIA_ERR_DTYPE;
@@ -293,8 +295,9 @@ LIA_EXPORT int lia_conv_state_update(const float* x, long long ld, float* state,
                                      const int* positions, const int* slots, int n_tokens, int channels, int taps, cudaStream_t stream) {
     if (n_tokens <= 0 || taps <= 1) return LIA_OK;
     if (channels <= 0 || taps > MAX_TAPS || ld < channels || !state) return LIA_ERR_SIZE;
-    const int threads = channels >= 1024 ? 256 : 128;
-    return lia_launch(conv_state_update_kernel, dim3(n_tokens), dim3(threads), 0, stream, x, ld, state, state_stride,
+    const int threads = 128;
+    const dim3 grid(n_tokens, n_tokens >= 512 ? 1 : min(16, (channels + threads - 1) / threads));
+    return lia_launch(conv_state_update_kernel, grid, dim3(threads), 0, stream, x, ld, state, state_stride,
                       positions, slots, n_tokens, channels, taps);
 }
 
