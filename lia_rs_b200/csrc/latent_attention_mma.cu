@@ -126,21 +126,34 @@ latent_attention_kernel(LatentParams p) {
         __syncthreads();                                     // this tile is there (at first: the queries too); the one before is used up
         if (tile + 1 < tile_hi) fetch(tile + 1, buffer ^ 1);
         // ---- scores of keys 8 warp .. 8 warp + 7 for the 16 rows ----
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        // four accumulators in turn: a product waits for the one before it only every fourth time
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
         {
             const uint32_t a_base = smem_addr(qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + (lane >> 4) * 8);
             const uint32_t b_base = smem_addr(ks + (warp * 8 + (lane & 7)) * ld + (lane >> 3) * 8);
-            for (int k0 = 0; k0 < dk; k0 += 32) {
+            for (int k0 = 0; k0 < dk; k0 += 64) {
                 uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
                 ldmatrix_x4(b_base + k0 * 2, b0, b1, b2, b3);               // k0..7, 8..15, 16..23, 24..31 of the 8 keys
                 ldmatrix_x4(a_base + k0 * 2, a0, a1, a2, a3);
-                mma_bf16(s, a0, a1, a2, a3, b0, b1);
+                mma_bf16(s0, a0, a1, a2, a3, b0, b1);
                 if (k0 + 16 < dk) {
                     ldmatrix_x4(a_base + (k0 + 16) * 2, a0, a1, a2, a3);
-                    mma_bf16(s, a0, a1, a2, a3, b2, b3);
+                    mma_bf16(s1, a0, a1, a2, a3, b2, b3);
+                }
+                if (k0 + 32 < dk) {
+                    ldmatrix_x4(b_base + (k0 + 32) * 2, b0, b1, b2, b3);
+                    ldmatrix_x4(a_base + (k0 + 32) * 2, a0, a1, a2, a3);
+                    mma_bf16(s2, a0, a1, a2, a3, b0, b1);
+                    if (k0 + 48 < dk) {
+                        ldmatrix_x4(a_base + (k0 + 48) * 2, a0, a1, a2, a3);
+                        mma_bf16(s3, a0, a1, a2, a3, b2, b3);
+                    }
                 }
             }
         }
+        float s[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] = (s0[e] + s1[e]) + (s2[e] + s3[e]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = g + (e >> 1) * 8, c = warp * 8 + tq * 2 + (e & 1);

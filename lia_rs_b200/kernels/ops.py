@@ -980,7 +980,7 @@ def gemm_simt_batched(mode, a, w, out, alpha: float = 1.0, label=None):
     N = out.shape[2]
     if tuple(w.shape) != (B, N, K) or tuple(out.shape) != (B, M, N):
         raise KernelError(f"gemm: shapes do not agree: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
-    with _timed("gemm_simt", label, work=lambda: _gemm_work(a.reshape(-1, K), w.reshape(-1, K), out.reshape(-1, N))):
+    with _timed("gemm_simt", label, work=lambda: _batched_work(a, w, out)):
         _check(lib().lia_gemm_simt_batched(mode, _p(a), dtype_code(a.dtype), a.stride(1), a.stride(0), _p(w),
                                            dtype_code(w.dtype), w.stride(1), w.stride(0), _p(out), dtype_code(out.dtype),
                                            out.stride(1), out.stride(0), B, M, N, K, alpha, _stream()), "gemm_simt_batched")
@@ -1014,6 +1014,13 @@ def latent_attention(q1, q2, latent_pages, part_pages, positions, slots, block_t
                                           latent_pages.shape[0], splits, _p(error_flag), _stream()), "latent_attention")
 
 
+def _batched_work(a, w, out):
+    """(bytes, flops) of B products as the roofline counts them: every operand once."""
+    B, M, K = a.shape
+    N = out.shape[2]
+    return (B * (M * K * a.element_size() + N * K * w.element_size() + M * N * out.element_size()), 2 * B * M * N * K)
+
+
 def _batched_arguments(a, w, out):
     for t in (a, w, out):
         if not t.is_cuda or t.dim() != 3 or t.stride(2) != 1:
@@ -1039,5 +1046,5 @@ def gemm_mma_batched(a, w, out, label=None):
     pointers, (B, M, N, K) = _batched_arguments(a, w, out)
     if not (a.dtype == w.dtype == out.dtype == torch.bfloat16):
         raise KernelError("gemm_mma_batched is a bfloat16 kernel")
-    with _timed("gemm_mma_batched", label, work=lambda: _gemm_work(a.reshape(-1, K), w.reshape(-1, K), out.reshape(-1, N))):
+    with _timed("gemm_mma_batched", label, work=lambda: _batched_work(a, w, out)):
         _check(lib().lia_gemm_mma_batched(*pointers, B, M, N, K, _stream()), "gemm_mma_batched")

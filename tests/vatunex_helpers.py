@@ -68,7 +68,7 @@ VATUNEX = {
         config={"architecture": "Vatunex", "vocab": 211, "width": 128, "norm": {"eps": 1e-6}, "initializer_range": 0.05,
                 "layers": [_attention(4, 1, 128, 128, 0.09, {"base": 25000.0, "dims": 64, "scaling":
                                                              {"factor": 2.0, "low": 2.0, "high": 8.0, "original": 32}}, True, None, 192),
-                           _latent(4, 64, 32, 64, 128, 64, 0.1, 40, 25000.0, 192),
+                           _latent(4, 64, 32, 48, 96, 64, 0.1, 40, 25000.0, 192),
                            _attention(4, 1, 128, 128, 0.09, {"base": 25000.0, "dims": 128}, True, None, 192),
                            _scan(256, 16, 8, 2, 192),
                            _attention(8, 2, 64, 64, 0.125, {"base": 1e6, "dims": 32}, False, 50, 64)]},
