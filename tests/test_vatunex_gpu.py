@@ -172,6 +172,37 @@ def test_the_roads_of_long_steps_on_short_ones(models, name, dtype, monkeypatch)
     vh.assert_close(np.concatenate(others), reference_other, dtype, f"{name} beside them, long roads", model["config"])
 
 
+@pytest.mark.parametrize("seed", range(101, 113))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Twelve configurations drawn at random (layer order, every size, every optional key): whole, in portions beside
+    another request's single tokens on reused pages, and token by token, in 32-bit against the plain model; whole and
+    portions in bfloat16."""
+    model = vh.make_model(str(tmp_path / "m"), f"random-{seed}")
+    tokens, other = tokens_of(model, 83, seed), tokens_of(model, 21, seed + 1)
+    reference, reference_other = vh.plain_logits(model, tokens), vh.plain_logits(model, other)
+    for dtype in DTYPES:
+        engine = make_engine(model, dtype, 128)
+        replay = helpers.Replayer(engine)
+        logits = replay.step([("w", tokens, range(len(tokens)))], end=["w"])
+        vh.assert_close(logits, reference, dtype, f"random {seed} whole", model["config"])
+        rows, others, at = [], [], 0
+        for i, size in enumerate([2, 19, 1, 33, 5, 23]):
+            batch = [("r", tokens[at:at + size], range(size))]
+            if i < len(other) // 4:
+                batch.append(("o", other[4 * i:4 * i + 4] if i % 2 else other[4 * i:4 * i + 1], range(4 if i % 2 else 1)))
+            out = replay.step(batch)
+            rows.append(out[:size])
+            if len(batch) > 1:
+                others.append(out[size:])
+            at += size
+        assert at == len(tokens)
+        vh.assert_close(np.concatenate(rows), reference, dtype, f"random {seed} portions", model["config"])
+        replay.step([], end=["r", "o"])
+        if dtype == "float32":
+            rows = [replay.step([("s", [t], [0])]) for t in tokens[:40]]
+            vh.assert_close(np.concatenate(rows), reference[:40], dtype, f"random {seed} token by token", model["config"])
+
+
 @pytest.mark.parametrize("name", ["vat-B", "vat-C"])
 def test_long_decoding(models, name):
     """400 tokens one by one behind a short prompt, bfloat16: state, windows and pages hold over hundreds of steps."""
