@@ -3,7 +3,7 @@ plain implementation (tests/plain_vatunex.py).
 
 The configurations differ in everything that config.json gives: widths and vocabularies; the order of the three kinds
 of layer (each kind first, last and alone somewhere); latent attention with 1, 2, 3 and 4 heads, ranks smaller and
-larger than the width, windows that are no multiple of the page size, one layer without a window; attention with 1, 2
+larger than the width, a model of scans alone, windows that are no multiple of the page size, one layer without a window; attention with 1, 2
 and 4 query heads per kv head, key and value head sizes equal and unequal, rotation of all, part or none of a head, band
 scaling present and absent, a window on one layer, value mixing in none, two or three layers; scans with 1 to 4 taps,
 state sizes from 3 to 24 (one to four lanes a channel) and ranks of 1 and more; layers without a feed-forward."""
@@ -79,6 +79,10 @@ VATUNEX = {
                            _scan(160, 3, 5, 2, None),
                            _latent(4, 24, 16, 40, 56, 32, 0.15, 17, 1000.0, 100)]},
         seed=4, page_size=16, sharpen=1.5),
+    "vat-E": dict(          # no attention at all: the engine runs without a page pool, on state slots alone
+        config={"architecture": "Vatunex", "vocab": 83, "width": 56, "norm": {"eps": 1e-5}, "initializer_range": 0.08,
+                "layers": [_scan(88, 6, 2, 3, 72), _scan(64, 10, 7, 5, None)]},
+        seed=5, page_size=8, sharpen=1.0),
 }
 
 
