@@ -118,6 +118,7 @@ struct Args {
     int stages, early, chunks, ck;   // ring; stages asked for before the tokens' rows; K chunks per block; elements of K per chunk (a multiple of 64)
     int blocks, x_pitch, stage_bytes, half_bytes;
     int norm, out_bf16;              // norm: 0 none, 1 weight bf16, 2 weight f32
+    int activation;                  // STORE only: 0 none, 1 GELU (tanh form), 2 SiLU, applied to alpha * sum before the store
     float alpha, eps;
     int* error_flag;
 };
@@ -368,7 +369,14 @@ gemm_stream_kernel(Args a) {
 #pragma unroll
                     for (int w = 0; w < MMA_WARPS; ++w) total += sums[buf][w][m][token];
                     if (token < a.M && f < a.N) {
-                        const float value = MODE == GEMM_STORE ? a.alpha * total : old[j] + a.alpha * total;
+                        float value = MODE == GEMM_STORE ? a.alpha * total : old[j] + a.alpha * total;
+                        if (MODE == GEMM_STORE && a.activation == 1) {
+                            // 0.5 z (1 + tanh(u)), u = sqrt(2/pi) (z + 0.044715 z^3), as z / (1 + exp(-2u))
+                            const float u = 0.7978845608028654f * (value + 0.044715f * value * value * value);
+                            value = value / (1.0f + expf(-2.0f * u));
+                        } else if (MODE == GEMM_STORE && a.activation == 2) {
+                            value = value / (1.0f + expf(-value));
+                        }
                         if (a.out_bf16) reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)token * a.ldo + f] = __float2bfloat16_rn(value);
                         else reinterpret_cast<float*>(a.out)[(size_t)token * a.ldo + f] = value;
                     }
@@ -714,11 +722,13 @@ LIA_EXPORT int lia_gemm_stream_stages(int mode, int M, int N, int K, int with_no
 // pointers that are not 16-byte aligned (bulk copies and 16-byte loads need both), and sizes whose rows do not
 // fit in shared memory beside a ring (ask lia_gemm_stream_stages first).  `stages_cap` > 0 limits the ring;
 // `early_stages` > 0 sets how many stages the producer asks for before the tokens' rows have been asked for (default 2).
+// `activation` (STORE only): 1 the tanh form of GELU, 2 SiLU, applied to the 32-bit result before it is stored.
 LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, int ldw, void* out, int out_dtype,
                                int ldo, int M, int N, int K, float alpha, const float* norm_src, int ld_norm,
                                const void* norm_weight, int norm_weight_dtype, float eps, int sms, int stages_cap,
-                               int early_stages, int* error_flag, cudaStream_t stream) {
+                               int early_stages, int activation, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return LIA_OK;
+    if (activation < 0 || activation > 2 || (activation && mode != GEMM_STORE)) return LIA_ERR_SIZE;
     if (M > TOKENS || K <= 0 || K % 64 || ldw % 8 || ldw < K || ldo < N || sms <= 0) return LIA_ERR_SIZE;
     if ((uintptr_t)W & 15u) return LIA_ERR_ALIGN;
     if (norm_src) {
@@ -737,6 +747,7 @@ LIA_EXPORT int lia_gemm_stream(int mode, const void* X, int ldx, const void* W, 
     a.norm_src = norm_src; a.norm_weight = norm_weight; a.ld_norm = ld_norm; a.eps = eps;
     a.norm = !norm_src ? 0 : (norm_weight_dtype == LIA_BF16 ? 1 : 2);
     a.out_bf16 = out_dtype == LIA_BF16;
+    a.activation = activation;
     a.ldw = ldw; a.ldx = ldx; a.ldo = ldo; a.M = M; a.N = N; a.K = K; a.alpha = alpha; a.error_flag = error_flag;
     chunking(K, &a.chunks, &a.ck);
     const long long blocks = mode == GEMM_SWIGLU ? (N + HALF_ROWS - 1) / HALF_ROWS : (N + ROWS - 1) / ROWS;

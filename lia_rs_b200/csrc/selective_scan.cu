@@ -4,7 +4,8 @@
 // the recurrence's state [channels, states].
 //
 //  * `causal_conv`: y_t[c] = act(bias[c] + sum_j taps[c, j] x_(t - n + 1 + j)[c]) (act: SiLU or none), inputs before the
-//    run taken from the slot's state, zeros before the sequence's start.  It reads the state and does not change it.
+//    run taken from the slot's state, zeros before the sequence's start.  It reads the state and does not change it,
+//    except in a step of single tokens only, where it can leave the new state itself.
 //  * `conv_state_update`: the slot's state becomes the last taps - 1 inputs up to the end of the run.  A kernel of its
 //    own, after the convolution: a run's first tokens read what its last tokens overwrite.
 //  * `selective_scan`: dt = softplus(dt_raw + dt_bias);  S[c, n] <- exp(dt[c] A[c, n]) S[c, n] + dt[c] x[c] B[n];
@@ -27,7 +28,7 @@ __device__ __forceinline__ int run_before(const int* __restrict__ positions, con
 }
 
 // input of channel c at distance k (>= 1) before row t, whose run has m rows before t
-__device__ __forceinline__ float input_before(const float* __restrict__ x, long long ld, const float* __restrict__ state,
+__device__ __forceinline__ float input_before(const float* __restrict__ x, long long ld, const float* state,
                                               int channels, int taps, int t, int pos, int m, int k, int c) {
     if (pos - k < 0) return 0.f;
     if (k <= m) return x[(size_t)(t - k) * ld + c];
@@ -36,10 +37,10 @@ __device__ __forceinline__ float input_before(const float* __restrict__ x, long 
 
 template <typename TO>
 __global__ void causal_conv_kernel(const float* __restrict__ x, long long ld, const float* __restrict__ taps_weight,
-                                   const float* __restrict__ bias, const float* __restrict__ state,
+                                   const float* __restrict__ bias, const float* state,
                                    long long state_stride, const int* __restrict__ positions, const int* __restrict__ slots,
                                    float* __restrict__ out, TO* __restrict__ out_copy, int n_tokens, int channels,
-                                   int taps, int act) {
+                                   int taps, int act, float* state_out) {           // (state_out, if given, IS state)
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -57,6 +58,18 @@ __global__ void causal_conv_kernel(const float* __restrict__ x, long long ld, co
         if (act == 1) y = y / (1.0f + expf(-y));
         out[(size_t)t * channels + c] = y;
         if (out_copy) out_copy[(size_t)t * channels + c] = from_float<TO>(y);
+        if (state_out) {
+            // A step of single tokens: nobody else reads this slot's state, so the thread that read a channel's inputs
+            // moves them up by one and appends its own, and no second kernel runs.
+            float* mine = state_out + (size_t)slot * state_stride;
+            float kept[MAX_TAPS];
+#pragma unroll
+            for (int i = 0; i < MAX_TAPS - 1; ++i)
+                if (i < taps - 1) kept[i] = i + 1 < taps - 1 ? mine[(size_t)(i + 1) * channels + c] : x[(size_t)t * ld + c];
+#pragma unroll
+            for (int i = 0; i < MAX_TAPS - 1; ++i)
+                if (i < taps - 1) mine[(size_t)i * channels + c] = kept[i];
+        }
     }
 }
 
@@ -274,20 +287,24 @@ scan_carry_kernel(ScanArgs p) {
 LIA_EXPORT int lia_causal_conv(const float* x, long long ld, const float* taps_weight, const float* bias,
                                const float* state, long long state_stride, const int* positions, const int* slots,
                                float* out, void* out_copy,
-                               int copy_dtype, int n_tokens, int channels, int taps, int act, cudaStream_t stream) {
+                               int copy_dtype, int n_tokens, int channels, int taps, int act, int update_single,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return LIA_OK;
     if (channels <= 0 || taps < 1 || taps > MAX_TAPS || ld < channels || (taps > 1 && !state) || act < 0 || act > 1)
         return LIA_ERR_SIZE;
     const int threads = 128;
     // few tokens: a token's channels over several CTAs, so that the step's rows fill the device
     const dim3 grid(n_tokens, n_tokens >= 512 ? 1 : min(16, (channels + threads - 1) / threads));
+    // `update_single`: every run of the step is a single token; the kernel then leaves the new state itself
+    float* state_out = (update_single && taps > 1) ? const_cast<float*>(state) : nullptr;
     if (!out_copy || copy_dtype == LIA_F32)
         return lia_launch(causal_conv_kernel<float>, grid, dim3(threads), 0, stream, x, ld, taps_weight, bias,
-                          state, state_stride, positions, slots, out, (float*)out_copy, n_tokens, channels, taps, act);
+                          state, state_stride, positions, slots, out, (float*)out_copy, n_tokens, channels, taps, act,
+                          state_out);
     if (copy_dtype == LIA_BF16)
         return lia_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, ld, taps_weight,
                           bias, state, state_stride, positions, slots, out, (__nv_bfloat16*)out_copy, n_tokens, channels,
-                          taps, act);
+                          taps, act, state_out);
     return LIA_ERR_DTYPE;
 }
 

@@ -62,7 +62,7 @@ class _Signatures:
     lia_gemm_skinny = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                        c_void_p, c_void_p]
     lia_gemm_stream = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                       c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p]
+                       c_void_p, c_int, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_gemm_stream_stages = [c_int, c_int, c_int, c_int, c_int, c_int]
     lia_attention_prefill = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
@@ -107,7 +107,7 @@ class _Signatures:
                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lia_causal_conv = [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p,
-                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lia_conv_state_update = [c_void_p, ctypes.c_longlong, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_void_p]
     lia_selective_scan = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_void_p,
@@ -434,10 +434,11 @@ def gemm_stream_accepts(mode, a, w, out, norm=False) -> bool:
 
 
 def gemm_stream(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None, norm_weight=None, eps: float = 0.0,
-                stages_cap: int = 0, early_stages: int = 0):
+                stages_cap: int = 0, early_stages: int = 0, activation: int = 0):
     """out[M, N] (op)= alpha * x[M, K] @ w[N, K]^T for M <= 16 tokens, one persistent CTA per SM with the
     tokens' rows resident in shared memory; see csrc/gemm_stream.cu.  Without `norm_weight`, x = a (bfloat16);
-    with it, a is 32-bit and x = RMSNorm(a; norm_weight, eps) rounded to bfloat16, computed inside the kernel."""
+    with it, a is 32-bit and x = RMSNorm(a; norm_weight, eps) rounded to bfloat16, computed inside the kernel.
+    `activation` (STORE only; ACT_GELU_TANH or ACT_SILU): applied to the 32-bit result before it is stored."""
     M, K = a.shape
     N = out.shape[1]
     if w.shape[1] != K or out.shape[0] != M or w.shape[0] != (2 * N if mode == GEMM_SWIGLU else N):
@@ -451,7 +452,8 @@ def gemm_stream(mode, a, w, out, alpha: float = 1.0, error_flag=None, label=None
         x, ldx, src, ld_src, nw, nw_code = None, 0, _p(a), a.stride(0), _p(norm_weight), dtype_code(norm_weight.dtype)
     with _timed("gemm_stream", label, work=lambda: _gemm_work(a, w, out)):
         _check(lib().lia_gemm_stream(mode, x, ldx, _p(w), w.stride(0), _p(out), dtype_code(out.dtype), out.stride(0),
-                                     M, N, K, alpha, src, ld_src, nw, nw_code, eps, sms, stages_cap, early_stages, _p(error_flag),
+                                     M, N, K, alpha, src, ld_src, nw, nw_code, eps, sms, stages_cap, early_stages, int(activation),
+                                     _p(error_flag),
                                      _stream()), "gemm_stream")
 
 
@@ -911,10 +913,11 @@ CONV_MAX_TAPS = 8
 SCAN_MAX_STATES = 256
 
 
-def causal_conv(x, taps_weight, bias, state, positions, slots, out, out_copy=None, act: int = 0):
+def causal_conv(x, taps_weight, bias, state, positions, slots, out, out_copy=None, act: int = 0, update_single: bool = False):
     """out[t, c] = act(bias[c] + sum_j taps[c, j] x[t - n + 1 + j, c]) along each request's run, earlier inputs from
     `state` [slots, n - 1, channels]; `x` 32-bit rows (any stride, the first `channels` columns); act 1: SiLU.  The
-    state is read, not changed: `conv_state_update` follows.  See csrc/selective_scan.cu."""
+    state is read, not changed: `conv_state_update` follows; except with `update_single` (every run of the step is a
+    single token), where the kernel leaves the new state itself.  See csrc/selective_scan.cu."""
     _cuda(taps_weight, bias, positions, slots, out, out_copy)
     _f32(x, taps_weight, bias, state, out)
     n, channels = out.shape
@@ -926,7 +929,7 @@ def causal_conv(x, taps_weight, bias, state, positions, slots, out, out_copy=Non
         _check(lib().lia_causal_conv(_p(x), x.stride(0), _p(taps_weight), _p(bias), _p(state),
                                      state.stride(0) if state is not None else 0, _p(positions), _p(slots),
                                      _p(out), _p(out_copy), dtype_code(out_copy.dtype) if out_copy is not None else F32, n,
-                                     channels, taps, int(act), _stream()), "causal_conv")
+                                     channels, taps, int(act), 1 if update_single else 0, _stream()), "causal_conv")
 
 
 def conv_state_update(x, state, positions, slots, channels: int):

@@ -51,9 +51,10 @@ class SwiGLU(FeedForward):
 @register_feed_forward("dense_act")
 class DenseActivation(FeedForward):
     """Dense feed-forward without a gate: f = Wd act(Wu x), no biases.  `activation`: "gelu_tanh"
-    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu" or "none".  The up product leaves 32-bit rows; the
-    activation is taken of those and rounded once to the compute element type; the down product adds into the residual
-    stream.  Parameters: hidden, intermediate, activation, and optionally `names`: the checkpoint names of the up and
+    (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), "silu" or "none".  The activation is taken of the up product's
+    32-bit result and rounded once to the compute element type: in the product's epilogue where the kernel can (the
+    few-token persistent product), else by a kernel of its own on the product's 32-bit rows; the down product adds into
+    the residual stream.  Parameters: hidden, intermediate, activation, and optionally `names`: the checkpoint names of the up and
     down matrices behind the part's prefix."""
     graph_safe = True
     takes_deferred_norm = True
@@ -93,7 +94,10 @@ class DenseActivation(FeedForward):
     def forward(self, ctx, x, residual, scale, store=False):
         rt, n = self.runtime, x.shape[0]
         up = ctx.buffer("ffn.up", (n, self.intermediate), torch.float32)
-        linear(rt, STORE, x, self.w_up, up, error_flag=ctx.error_flag, name="up")
         act = ctx.buffer("ffn.act", (n, self.intermediate), rt.compute_dtype)
-        rt.ops.activation_rows(up, act, self.activation)
+        if self.activation == 0:
+            linear(rt, STORE, x, self.w_up, act, error_flag=ctx.error_flag, name="up")
+        elif not linear(rt, STORE, x, self.w_up, act, error_flag=ctx.error_flag, name="up", activation=self.activation,
+                        unactivated=up):
+            rt.ops.activation_rows(up, act, self.activation)
         linear(rt, STORE if store else ACCUM, act, self.w_down, residual, scale, error_flag=ctx.error_flag, name="down")

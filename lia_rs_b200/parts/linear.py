@@ -58,10 +58,16 @@ def _choose(mode, a, w, out) -> int:
 
 
 def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
-           error_flag=None, name=None):
+           error_flag=None, name=None, activation: int = 0, unactivated: torch.Tensor = None):
     """`name`: what the product is to its caller ("qkv", "down", ...), for the per-kernel-class profile.
     `error_flag` (int32[1] on the device, a step's `ctx.error_flag`): a tensor-core kernel that gives up on one
-    of its bounded waits raises it to 3, and the step's caller then learns that the result is not to be used."""
+    of its bounded waits raises it to 3, and the step's caller then learns that the result is not to be used.
+    `activation` (STORE only; `ops.ACT_GELU_TANH`, `ops.ACT_SILU`): out = act(alpha a w^T).  The few-token persistent
+    kernel applies it in its epilogue and the call returns True; where another kernel serves the product, the plain
+    product goes to `unactivated` (32-bit rows of out's shape) instead of `out`, the call returns False and the
+    activation is the caller's (`ops.activation_rows`): nothing is rounded ahead of the activation either way."""
+    if activation and (mode != STORE or unactivated is None):
+        raise ValueError("an activation rides on a STORE product and needs 32-bit rows for the kernels that cannot apply it")
     if isinstance(a, DeferredNorm):
         # few tokens of a norm that a product kernel can apply itself: the norm's own kernel does not run
         record = a.norm.rms_record() if a.source.shape[0] <= ops.STREAM_MAX_TOKENS and w.dtype == torch.bfloat16 else None
@@ -75,18 +81,25 @@ def linear(runtime, mode: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tens
                                          and norm_weight.dtype in (torch.bfloat16, torch.float32)
                                          and ops.gemm_stream_accepts(mode, source, w, out, norm=True))
             if fused:
-                ops.gemm_stream(mode, source, w, out, alpha, error_flag, label=name, norm_weight=norm_weight, eps=eps)
-                return
+                ops.gemm_stream(mode, source, w, out, alpha, error_flag, label=name, norm_weight=norm_weight, eps=eps,
+                                activation=activation)
+                return bool(activation)
         a = a.tensor()
     if a.dtype != torch.bfloat16:
-        ops.gemm_simt(mode, a, w, out, alpha, label=name)
-        return
+        ops.gemm_simt(mode, a, w, unactivated if activation else out, alpha, label=name)
+        return False
     # everything the kernels' acceptance looks at: sizes, row strides, element types, 16-byte alignment of the bases
     key = (mode, a.shape, a.stride(), a.data_ptr() & 15, w.shape, w.stride(), w.dtype, w.data_ptr() & 15,
            out.shape[1], out.stride(), out.dtype, out.data_ptr() & 15, a.device.index)
     choice = _choices.get(key)
     if choice is None:
         choice = _choices[key] = _choose(mode, a, w, out)
+    if activation:
+        if choice == _STREAM:
+            ops.gemm_stream(mode, a, w, out, alpha, error_flag, label=name, activation=activation)
+            return True
+        linear(runtime, mode, a, w, unactivated, alpha, error_flag=error_flag, name=name)
+        return False
     if choice == _TC:
         ops.gemm_tc(mode, a, w, out, alpha, error_flag, label=name)
     elif choice == _STREAM:

@@ -92,8 +92,10 @@ class SelectiveScan(Mixer):
         linear(rt, STORE, x, self.w_in, uz, error_flag=flag, name="in")
         u = ctx.buffer("scan.u", (n, inner), torch.float32)
         u_rounded = ctx.buffer("scan.u_rounded", (n, inner), dtype) if dtype != torch.float32 else None
-        ops.causal_conv(uz, self.conv, self.conv_bias, conv_state, ctx.positions, ctx.slots, u, u_rounded, act=1)
-        if taps > 1:
+        single = ctx.decode_only                  # single tokens only: the convolution leaves its new state itself
+        ops.causal_conv(uz, self.conv, self.conv_bias, conv_state, ctx.positions, ctx.slots, u, u_rounded, act=1,
+                        update_single=single)
+        if taps > 1 and not single:
             ops.conv_state_update(uz, conv_state, ctx.positions, ctx.slots, inner)
         projected = ctx.buffer("scan.x", (n, rank + 2 * states), torch.float32)
         linear(rt, STORE, u if u_rounded is None else u_rounded, self.w_x, projected, error_flag=flag, name="x")

@@ -273,8 +273,10 @@ def test_causal_conv_carries_its_inputs_over_steps(taps):
         n = x.shape[0]
         out, copy = torch.empty(n, channels, device="cuda"), torch.empty(n, channels, dtype=torch.bfloat16, device="cuda")
         xd = dev(x)
-        ops.causal_conv(xd, dev(weight), dev(bias), state if taps > 1 else None, positions, slots, out, copy, act=1)
-        if taps > 1:
+        single = all(count == 1 for _, count in step)                  # then the convolution leaves the new state itself
+        ops.causal_conv(xd, dev(weight), dev(bias), state if taps > 1 else None, positions, slots, out, copy, act=1,
+                        update_single=single)
+        if taps > 1 and not single:
             ops.conv_state_update(xd, state, positions, slots, channels)
         row = 0
         for r, count in step:
@@ -362,3 +364,39 @@ def test_products_of_many_heads_on_the_tensor_cores(B, M, N, K):
     ops.gemm_mma_batched(dev(a), dev(w), side_by_side.view(M, B, N).transpose(0, 1))
     assert torch.equal(side_by_side.view(M, B, N).transpose(0, 1), planes)
     assert not ops.gemm_mma_batched_accepts(dev(a)[:, :, :K - 1], dev(w)[:, :, :K - 1], planes)      # K no multiple of 8
+
+
+@pytest.mark.parametrize("M", [1, 8, 16])
+def test_activation_in_the_few_token_products_epilogue(M):
+    """The persistent few-token product with GELU or SiLU in its epilogue against the activation of the plain product,
+    with and without the norm of its input rows inside the kernel; `linear` hands the product to 32-bit rows where
+    another kernel serves it (more tokens) and says so."""
+    from lia_rs_b200.kernels import ops
+    from lia_rs_b200.parts import Runtime
+    from lia_rs_b200.parts.linear import STORE, linear
+    g = torch.Generator().manual_seed(60 + M)
+    N, K = 328, 256
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.1).to(torch.bfloat16)
+    product = a.to(F64) @ w.to(F64).T
+    for act, plain in [(ops.ACT_GELU_TANH, pv.gelu_tanh), (ops.ACT_SILU, lambda z: z * torch.sigmoid(z))]:
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        assert ops.gemm_stream_accepts(ops.GEMM_STORE, dev(a), dev(w), out)
+        ops.gemm_stream(ops.GEMM_STORE, dev(a), dev(w), out, 0.5, activation=act)
+        assert torch.allclose(out.float().cpu().to(F64), plain(0.5 * product), atol=2e-2, rtol=1e-2)
+        rows = torch.randn(M, K, generator=g) * 2
+        weight = 1 + 0.2 * torch.randn(K, generator=g)
+        normed = pv.norm_plain(rows.to(F64), weight, 1e-5).to(torch.bfloat16).to(F64)
+        ops.gemm_stream(ops.GEMM_STORE, dev(rows), dev(w), out, 1.0, norm_weight=dev(weight), eps=1e-5, activation=act)
+        assert torch.allclose(out.float().cpu().to(F64), plain(normed @ w.to(F64).T), atol=3e-2, rtol=2e-2)
+    runtime = Runtime("cuda:0", torch.bfloat16)
+    for tokens, applied in [(M, True), (200, False)]:
+        a = torch.randn(tokens, K, generator=g).to(torch.bfloat16)
+        out = torch.zeros(tokens, N, dtype=torch.bfloat16, device="cuda")
+        wide = torch.zeros(tokens, N, dtype=torch.float32, device="cuda")
+        assert bool(linear(runtime, STORE, dev(a), dev(w), out, activation=ops.ACT_GELU_TANH, unactivated=wide)) == applied
+        want = a.to(F64) @ w.to(F64).T
+        if applied:
+            assert torch.allclose(out.float().cpu().to(F64), pv.gelu_tanh(want), atol=2e-2, rtol=1e-2)
+        else:
+            assert torch.allclose(wide.cpu().to(F64), want, atol=1e-3, rtol=1e-3) and float(out.abs().max()) == 0.0
