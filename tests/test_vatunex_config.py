@@ -121,7 +121,7 @@ def test_random_weights_pass_the_loader(tmp_path, name):
 
 
 def test_band_scaled_frequencies_against_the_plain_ones():
-    for base, dims, scaling in [(10000.0, 16, None), (20000.0, 24, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}),
+    for base, dims, scaling in [(10000.0, 16, None), (30000.0, 20, {"factor": 3.0, "low": 1.0, "high": 6.0, "original": 256}),
                                 (500.0, 64, {"factor": 8.0, "low": 0.5, "high": 16.0, "original": 100}),
                                 (1e6, 128, {"factor": 2.0, "low": 2.0, "high": 8.0, "original": 32})]:
         ours = band_scaled_frequencies(base, dims, scaling)

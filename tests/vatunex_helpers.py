@@ -91,7 +91,7 @@ def random_configuration(seed: int) -> dict:
     multiples of 8, 16 or 32, every optional key present or absent."""
     import random
     rng = random.Random(seed)
-    width = rng.choice([48, 64, 72, 96, 128, 136])
+    width = rng.choice([48, 64, 72, 96, 128, 144])
     if seed % 3 == 0:
         width = random.Random(seed).choice([50, 66, 100, 257])          # rows that no 16-byte access fits
     mixing = (rng.choice([1, 2]), rng.choice([8, 16, 24, 32]))            # kv heads and value size of the layers that mix values
